@@ -1,0 +1,145 @@
+/*
+ * awq_b200.h -- C ABI of libawq_b200.so: AWQ W4A16 linear and fused-MoE kernels for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (cudaStream_t passed
+ * as void*); no framework types cross this boundary.  The caller owns every buffer,
+ * including scratch; the library allocates nothing, keeps no pointer after the call returns
+ * and never synchronises the stream.  All work is enqueued on `stream`.
+ *
+ * Return value: AWQ_B200_OK (0) or a negative AWQ_B200_ERR_* code.  Arguments are validated on
+ * the host before anything is launched; a kernel never traps.
+ *
+ * Tensor conventions (identical to vLLM's AWQ checkpoints; paths below are inside the vllm
+ * package, version 0.22.0, which is the arithmetic the cloudrift-ai/server-benchmark harness
+ * measures through the `vllm/vllm-openai` image: utils/generate_compose.py:65-100,
+ * benchmarks/3_vllm_benchmark.sh:151-162):
+ *   qweight int32 [K, N/8]      8 int4 per word along N, nibble p (LSB first) = column
+ *                               [0,2,4,6,1,3,5,7][p] of the word's 8 columns
+ *   qzeros  int32 [K/G, N/8]    same packing
+ *   scales  fp16  [K/G, N]
+ *   W[k][n] = (q[k][n] - z[k/G][n]) * s[k/G][n]
+ *   (model_executor/layers/quantization/awq.py:182-255, awq_triton.py:54-101)
+ */
+#ifndef AWQ_B200_H_
+#define AWQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AWQ_B200_OK 0
+#define AWQ_B200_ERR_NULL (-1)      /* a required pointer is NULL */
+#define AWQ_B200_ERR_SHAPE (-2)     /* a size is non-positive or violates a divisibility rule */
+#define AWQ_B200_ERR_ALIGN (-3)     /* a pointer is not 16-byte aligned */
+#define AWQ_B200_ERR_GROUP (-4)     /* unsupported quantisation group size */
+#define AWQ_B200_ERR_WORKSPACE (-5) /* scratch buffer missing or too small */
+#define AWQ_B200_ERR_LAUNCH (-6)    /* the CUDA runtime refused a launch */
+#define AWQ_B200_ERR_DEVICE (-7)    /* current device is not compute capability 10.x */
+#define AWQ_B200_ERR_DRIVER (-8)    /* a driver entry point (tensor-map encode) is unavailable */
+#define AWQ_B200_ERR_LIMIT (-9)     /* a size exceeds a fixed built-in capacity */
+
+/* Human-readable text for a return code.  Never NULL. */
+const char* awq_b200_strerror(int code);
+
+/* Library version, "major.minor". */
+const char* awq_b200_version(void);
+
+/*
+ * W fp16 [K, N] = (q - z) * s, the product rounded once to fp16.
+ * Replaces torch.ops._C.awq_dequantize(qweight, scales, zeros, split_k_iters, thx, thy)
+ * (vllm/_custom_ops.py:542-556; called from quantization/awq.py:280).
+ * Requires N % 8 == 0, K % group == 0, group % 8 == 0.
+ */
+int awq_b200_dequantize(const void* qweight, const void* scales, const void* qzeros, void* out,
+                        int K, int N, int group, void* stream);
+
+/*
+ * y fp16 [M, N] = x fp16 [M, K] @ W, fp32 accumulation, optional fp16 bias [N] added before
+ * the final rounding (bias may be NULL).
+ * Replaces torch.ops._C.awq_gemm(input, qweight, scales, qzeros, split_k_iters)
+ * (vllm/_custom_ops.py:576-587; called from quantization/awq.py:283) and the
+ * awq_dequantize + torch.matmul pair used for >= 256 tokens (awq.py:276-281): one entry
+ * point serves every M, picking a weight-streaming kernel or a tcgen05 kernel by M.
+ * `kernel` selects the implementation: AWQ_B200_KERNEL_AUTO or one of the explicit ids (a
+ * request the shape does not permit returns AWQ_B200_ERR_SHAPE).
+ * Scratch: awq_b200_gemm_workspace_bytes(M, N, K, group, kernel) bytes, 256-byte aligned; may
+ * be NULL when that size is 0.
+ */
+#define AWQ_B200_KERNEL_AUTO 0
+#define AWQ_B200_KERNEL_GENERIC 1  /* CUDA-core reference kernel, any legal shape */
+#define AWQ_B200_KERNEL_STREAM 2   /* small-M weight-streaming kernel (mma.sync, cluster split-K) */
+#define AWQ_B200_KERNEL_TCGEN05 3  /* large-M tcgen05/TMEM kernel with in-smem dequantisation */
+#define AWQ_B200_KERNEL_STREAM_EXACT 4 /* small-M kernel with the magic-number conversion */
+
+size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel);
+
+int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const void* qzeros,
+                  const void* bias, void* out, int M, int N, int K, int group, int kernel,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Router: softmax over E experts, top-k (ties: lower expert id first), optional
+ * renormalisation of the k weights.  gating is fp32 (gating_dtype 0) or fp16 (1), [T, E].
+ * Outputs: topk_weights fp32 [T, k], topk_ids int32 [T, k], token_expert_indices int32 [T, k]
+ * (= slot * T + token; may be NULL).
+ * Replaces torch.ops._moe_C.topk_softmax (vllm/_custom_ops.py:2370-2385;
+ * fused_moe/router/fused_topk_router.py:17-33).  Requires E <= 1024, k <= 32, k <= E.
+ */
+int awq_b200_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
+                          int renormalize, float* topk_weights, int32_t* topk_ids,
+                          int32_t* token_expert_indices, void* stream);
+
+/*
+ * Token -> expert permutation (stable counting sort).  sorted_ids receives the flat
+ * (token * topk + slot) indices grouped by expert in ascending flat index, each expert's run
+ * padded to a multiple of `block` with the sentinel T*topk; every remaining entry up to
+ * `sorted_capacity` is the sentinel too.  expert_ids[b] is the expert of block b (-1 past the
+ * used blocks), num_post_pad[0] the padded total.  expert_map (may be NULL) maps global to
+ * local expert ids, -1 = not on this rank (those entries are dropped).
+ * sorted_capacity must be >= awq_b200_moe_sorted_capacity(T * topk, E, block);
+ * expert_ids holds ceil(sorted_capacity / block) entries.
+ * Replaces torch.ops._moe_C.moe_align_block_size (vllm/_custom_ops.py:2247-2264;
+ * fused_moe/moe_align_block_size.py:11-103).  Requires E <= 1024, T * topk <= 2^24.
+ */
+int64_t awq_b200_moe_sorted_capacity(int64_t numel, int E, int block);
+
+int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int E, int block,
+                                  const int32_t* expert_map, int32_t* sorted_ids,
+                                  int64_t sorted_capacity, int32_t* expert_ids,
+                                  int32_t* num_post_pad, void* stream);
+
+/*
+ * AWQ fused-MoE experts: for every (token, slot) gate_up GEMM -> silu(gate) * up -> down GEMM
+ * -> times routed weight -> sum over slots into out fp16 [T, H].
+ *   w13_q int32 [E, H, 2I/8], w13_s fp16 [E, H/G, 2I], w13_z int32 [E, H/G, 2I/8]
+ *   w2_q  int32 [E, I, H/8],  w2_s  fp16 [E, I/G, H],  w2_z  int32 [E, I/G, H/8]
+ * (parameter layout: quantization/awq_marlin.py:549-623).  sorted_ids / expert_ids /
+ * num_post_pad are the outputs of awq_b200_moe_align_block_size with block =
+ * awq_b200_moe_block_size(T, topk, E).
+ * Replaces fused_experts / fused_experts_impl (fused_moe/fused_moe.py:1587-1631,1664-1869)
+ * and the Marlin expert path (fused_moe/experts/marlin_moe.py:225-262).
+ * E is the number of stacked (local) experts.  expert_parallel != 0 says sorted_ids was built
+ * with an expert_map, i.e. some (token, slot) pairs have no expert here and contribute zero.
+ * Scratch: awq_b200_moe_workspace_bytes(T, topk, E_global, H, I) bytes, 256-byte aligned.
+ * Requires H % 128 == 0, I % 128 == 0, group in {32, 64, 128}.
+ */
+int awq_b200_moe_block_size(int T, int topk, int E);
+
+size_t awq_b200_moe_workspace_bytes(int T, int topk, int E, int H, int I);
+
+int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, const void* w13_z,
+                         const void* w2_q, const void* w2_s, const void* w2_z,
+                         const float* topk_weights, const int32_t* sorted_ids,
+                         const int32_t* expert_ids, const int32_t* num_post_pad, void* out,
+                         int T, int topk, int E, int H, int I, int group, int block,
+                         int expert_parallel, int64_t sorted_capacity, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AWQ_B200_H_ */

@@ -1,0 +1,105 @@
+"""Layer-level API mirroring vLLM's AWQ linear method (paths inside the ``vllm`` package):
+
+  AWQConfig            model_executor/layers/quantization/awq.py:36-107
+  AWQLinearMethod      model_executor/layers/quantization/awq.py:172-286
+      create_weights   :182-255   parameter contract (qweight / qzeros / scales shapes, checks)
+      apply            :262-286   y = x @ dequant(W) (+ bias), output shape x.shape[:-1] + (N,)
+
+Difference from the reference: ``apply`` never materialises the fp16 weight matrix; one fused
+kernel family serves every token count (the reference switches to dequantize + matmul at 256
+tokens, awq.py:276-281).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+
+
+@dataclass
+class AWQConfig:
+    """weight_bits is fixed at 4; pack_factor = 32 / weight_bits = 8 (awq.py:50-63)."""
+
+    weight_bits: int = 4
+    group_size: int = 128
+    zero_point: bool = True
+
+    def __post_init__(self) -> None:
+        if self.weight_bits != 4:
+            raise ValueError("Currently, only 4-bit weight quantization is supported for AWQ, "
+                             f"but got {self.weight_bits} bits.")
+        if not self.zero_point:
+            raise ValueError("AWQ checkpoints without zero points are not supported")
+        self.pack_factor = 32 // self.weight_bits
+
+    @staticmethod
+    def get_supported_act_dtypes() -> list[torch.dtype]:
+        return [torch.half]
+
+    @staticmethod
+    def get_min_capability() -> int:
+        return 100  # sm_100a only
+
+
+class AWQLinear(torch.nn.Module):
+    """Bare parameter holder, the role LinearBase plays for quant_method.create_weights."""
+
+    def __init__(self) -> None:
+        super().__init__()
+
+
+class AWQLinearMethod:
+    """Linear method for AWQ on B200."""
+
+    def __init__(self, quant_config: AWQConfig):
+        self.quant_config = quant_config
+
+    def create_weights(self, layer: torch.nn.Module, input_size_per_partition: int,
+                       output_partition_sizes: list[int], input_size: int, output_size: int,
+                       params_dtype: torch.dtype, device: torch.device | str = "cuda",
+                       **extra_weight_attrs) -> None:
+        group_size = self.quant_config.group_size
+        if group_size == -1:
+            group_size = input_size
+        if input_size_per_partition % group_size != 0:
+            raise ValueError(
+                "The input size is not aligned with the quantized weight shape. This can be "
+                "caused by too large tensor parallel size.")
+        output_size_per_partition = sum(output_partition_sizes)
+        if output_size_per_partition % self.quant_config.pack_factor != 0:
+            raise ValueError(
+                "The output size is not aligned with the quantized weight shape. This can be "
+                "caused by too large tensor parallel size.")
+        if params_dtype != torch.float16:
+            raise ValueError("AWQ supports fp16 activations only")
+        pf = self.quant_config.pack_factor
+        mk = lambda *shape, dtype: torch.nn.Parameter(  # noqa: E731
+            torch.empty(*shape, dtype=dtype, device=device), requires_grad=False)
+        layer.register_parameter(
+            "qweight", mk(input_size_per_partition, output_size_per_partition // pf,
+                          dtype=torch.int32))
+        layer.register_parameter(
+            "qzeros", mk(input_size_per_partition // group_size, output_size_per_partition // pf,
+                         dtype=torch.int32))
+        layer.register_parameter(
+            "scales", mk(input_size_per_partition // group_size, output_size_per_partition,
+                         dtype=params_dtype))
+        layer.group_size = group_size
+
+    def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
+        for name in ("qweight", "qzeros", "scales"):
+            p = getattr(layer, name)
+            setattr(layer, name, torch.nn.Parameter(p.data.contiguous(), requires_grad=False))
+
+    def apply(self, layer: torch.nn.Module, x: torch.Tensor,
+              bias: torch.Tensor | None = None) -> torch.Tensor:
+        qweight, scales, qzeros = layer.qweight, layer.scales, layer.qzeros
+        pack_factor = self.quant_config.pack_factor
+        out_shape = x.shape[:-1] + (qweight.shape[-1] * pack_factor,)
+        reshaped_x = x.reshape(-1, x.shape[-1])
+        if not reshaped_x.is_contiguous():
+            reshaped_x = reshaped_x.contiguous()
+        out = ops.awq_gemm(reshaped_x, qweight, scales, qzeros, pack_factor, bias=bias)
+        return out.reshape(out_shape)

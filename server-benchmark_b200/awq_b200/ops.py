@@ -1,0 +1,248 @@
+"""Operator-level API: same names, argument order and meaning as the vLLM ops the
+cloudrift-ai/server-benchmark harness exercises (paths are inside the ``vllm`` package):
+
+  awq_gemm(input, qweight, scales, qzeros, split_k_iters)      _custom_ops.py:576-587
+  awq_dequantize(qweight, scales, zeros, split_k_iters, thx, thy)   _custom_ops.py:542-556
+  fused_topk(hidden_states, gating_output, topk, renormalize, ...)
+                                        model_executor/layers/fused_moe/router/fused_topk_router.py:69-113
+  moe_align_block_size(topk_ids, block_size, num_experts, expert_map, ...)
+                                        model_executor/layers/fused_moe/moe_align_block_size.py:11-103
+  fused_experts(hidden_states, w1, w2, topk_weights, topk_ids, ...)
+                                        model_executor/layers/fused_moe/fused_moe.py:1587-1631
+
+Every function launches hand-written sm_100a kernels through the C ABI on the current CUDA
+stream; nothing here computes on the CPU and nothing synchronises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+PACK_FACTOR = 8
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(t: torch.Tensor, name: str, dtype, ndim: int | None = None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name} must have {ndim} dimensions, got {t.dim()}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _awq_dims(qweight, scales, qzeros):
+    _require(qweight, "qweight", torch.int32, 2)
+    _require(scales, "scales", torch.float16, 2)
+    _require(qzeros, "qzeros", torch.int32, 2)
+    k, words = qweight.shape
+    n = words * PACK_FACTOR
+    groups = scales.shape[0]
+    if groups == 0 or k == 0 or k % groups != 0:
+        raise ValueError(f"K={k} is not a multiple of the number of groups {groups}")
+    if tuple(scales.shape) != (groups, n):
+        raise ValueError(f"scales must be [{groups}, {n}], got {tuple(scales.shape)}")
+    if tuple(qzeros.shape) != (groups, words):
+        raise ValueError(f"qzeros must be [{groups}, {words}], got {tuple(qzeros.shape)}")
+    return k, n, k // groups
+
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    """Scratch owned by the torch caching allocator, grown on demand, one per (device, stream)."""
+    if nbytes == 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def awq_dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
+                   split_k_iters: int = 0, thx: int = 0, thy: int = 0) -> torch.Tensor:
+    """W fp16 [K, N] = (q - z) * s.  ``split_k_iters``, ``thx``, ``thy`` are accepted for
+    signature compatibility (callers pass 0, 0, 0: quantization/awq.py:280) and ignored."""
+    k, n, group = _awq_dims(qweight, scales, zeros)
+    out = torch.empty((k, n), dtype=scales.dtype, device=qweight.device)
+    rc = _lib.load().awq_b200_dequantize(qweight.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                         out.data_ptr(), k, n, group, _stream())
+    _lib.check("awq_b200_dequantize", rc)
+    return out
+
+
+def awq_gemm(input: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
+             qzeros: torch.Tensor, split_k_iters: int = 8, *, bias: torch.Tensor | None = None,
+             kernel: int = _lib.KERNEL_AUTO) -> torch.Tensor:
+    """y fp16 [M, N] = input [M, K] @ dequant(qweight), fp32 accumulation.
+
+    ``split_k_iters`` is accepted and ignored (the split along K is chosen from the shape and
+    the SM count).  ``bias`` and ``kernel`` are keyword-only extensions.
+    """
+    k, n, group = _awq_dims(qweight, scales, qzeros)
+    _require(input, "input", torch.float16, 2)
+    if input.shape[1] != k:
+        raise ValueError(f"input has K={input.shape[1]}, qweight has K={k}")
+    if bias is not None:
+        _require(bias, "bias", torch.float16, 1)
+        if bias.shape[0] != n:
+            raise ValueError(f"bias must have {n} elements")
+    m = input.shape[0]
+    out = torch.empty((m, n), dtype=torch.float16, device=input.device)
+    if m == 0:
+        return out
+    lib = _lib.load()
+    need = lib.awq_b200_gemm_workspace_bytes(m, n, k, group, kernel)
+    ws = _workspace(input.device, need)
+    rc = lib.awq_b200_gemm(input.data_ptr(), qweight.data_ptr(), scales.data_ptr(),
+                           qzeros.data_ptr(), bias.data_ptr() if bias is not None else None,
+                           out.data_ptr(), m, n, k, group, kernel,
+                           ws.data_ptr() if ws is not None else None,
+                           ws.numel() if ws is not None else 0, _stream())
+    _lib.check("awq_b200_gemm", rc)
+    return out
+
+
+# ------------------------------------------------------------------------------- MoE
+
+
+def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: int,
+               renormalize: bool, indices_type: torch.dtype | None = None,
+               scoring_func: str = "softmax"):
+    """softmax -> top-k -> optional renormalise.  Returns (topk_weights f32 [T,k],
+    topk_ids i32 [T,k], token_expert_indices i32 [T,k])."""
+    if scoring_func != "softmax":
+        raise ValueError(f"Unsupported scoring function: {scoring_func}")
+    if hidden_states.shape[0] != gating_output.shape[0]:
+        raise ValueError("Number of tokens mismatch")
+    if indices_type not in (None, torch.int32):
+        raise ValueError("indices_type must be torch.int32")
+    if gating_output.dtype == torch.float32:
+        gd = 0
+    elif gating_output.dtype == torch.float16:
+        gd = 1
+    else:
+        raise ValueError("gating_output must be float32 or float16")
+    _require(gating_output, "gating_output", gating_output.dtype, 2)
+    t, e = gating_output.shape
+    dev = gating_output.device
+    w = torch.empty((t, topk), dtype=torch.float32, device=dev)
+    ids = torch.empty((t, topk), dtype=torch.int32, device=dev)
+    tok = torch.empty((t, topk), dtype=torch.int32, device=dev)
+    if t > 0:
+        rc = _lib.load().awq_b200_topk_softmax(gating_output.data_ptr(), gd, t, e, topk,
+                                               int(bool(renormalize)), w.data_ptr(),
+                                               ids.data_ptr(), tok.data_ptr(), _stream())
+        _lib.check("awq_b200_topk_softmax", rc)
+    return w, ids, tok
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int,
+                         expert_map: torch.Tensor | None = None, pad_sorted_ids: bool = False,
+                         ignore_invalid_experts: bool = False):
+    """Token -> expert permutation.  Returns (sorted_token_ids, expert_ids,
+    num_tokens_post_padded), all int32 on the device."""
+    _require(topk_ids, "topk_ids", torch.int32, 2)
+    lib = _lib.load()
+    t, k = topk_ids.shape
+    cap = int(lib.awq_b200_moe_sorted_capacity(t * k, num_experts, block_size))
+    if pad_sorted_ids:
+        cap = -(-cap // block_size) * block_size
+    dev = topk_ids.device
+    sorted_ids = torch.empty((cap,), dtype=torch.int32, device=dev)
+    nblk = -(-cap // block_size) if cap > 0 else 0
+    expert_ids = torch.empty((nblk,), dtype=torch.int32, device=dev)
+    num_post = torch.empty((1,), dtype=torch.int32, device=dev)
+    emap = None
+    if expert_map is not None and ignore_invalid_experts:
+        _require(expert_map, "expert_map", torch.int32, 1)
+        emap = expert_map
+    rc = lib.awq_b200_moe_align_block_size(topk_ids.data_ptr(), t, k, num_experts, block_size,
+                                           emap.data_ptr() if emap is not None else None,
+                                           sorted_ids.data_ptr(), cap, expert_ids.data_ptr(),
+                                           num_post.data_ptr(), _stream())
+    _lib.check("awq_b200_moe_align_block_size", rc)
+    if expert_map is not None and not ignore_invalid_experts:
+        # same post-processing as the reference wrapper (moe_align_block_size.py:100-101);
+        # unused trailing blocks stay -1
+        used = expert_ids >= 0
+        expert_ids = torch.where(used, expert_map[expert_ids.clamp(min=0).long()].to(torch.int32),
+                                 expert_ids)
+    return sorted_ids, expert_ids, num_post
+
+
+def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tensor,
+                  topk_ids: torch.Tensor, inplace: bool = False, activation: str = "silu",
+                  apply_router_weight_on_input: bool = False, global_num_experts: int = -1,
+                  expert_map: torch.Tensor | None = None, group_size: int = 128) -> torch.Tensor:
+    """AWQ fused-MoE experts.  ``w1`` and ``w2`` are (qweight, scales, qzeros) triples of the
+    stacked AWQ tensors: w1 = (i32 [E,H,2I/8], f16 [E,H/G,2I], i32 [E,H/G,2I/8]),
+    w2 = (i32 [E,I,H/8], f16 [E,I/G,H], i32 [E,I/G,H/8]).  Returns fp16 [T, H]."""
+    if activation != "silu":
+        raise ValueError("only the silu activation is implemented")
+    if apply_router_weight_on_input:
+        raise ValueError("apply_router_weight_on_input is not implemented")
+    w13_q, w13_s, w13_z = w1
+    w2_q, w2_s, w2_z = w2
+    _require(hidden_states, "hidden_states", torch.float16, 2)
+    _require(w13_q, "w1.qweight", torch.int32, 3)
+    _require(w13_s, "w1.scales", torch.float16, 3)
+    _require(w13_z, "w1.qzeros", torch.int32, 3)
+    _require(w2_q, "w2.qweight", torch.int32, 3)
+    _require(w2_s, "w2.scales", torch.float16, 3)
+    _require(w2_z, "w2.qzeros", torch.int32, 3)
+    _require(topk_weights, "topk_weights", torch.float32, 2)
+    _require(topk_ids, "topk_ids", torch.int32, 2)
+    t, h = hidden_states.shape
+    e = w13_q.shape[0]
+    inter = w2_q.shape[1]
+    topk = topk_ids.shape[1]
+    g = group_size
+    if w13_q.shape != (e, h, 2 * inter // 8) or w2_q.shape != (e, inter, h // 8):
+        raise ValueError("expert weight shapes do not match hidden/intermediate sizes")
+    if w13_s.shape != (e, h // g, 2 * inter) or w13_z.shape != (e, h // g, 2 * inter // 8):
+        raise ValueError("w1 scales/zeros shapes do not match group size")
+    if w2_s.shape != (e, inter // g, h) or w2_z.shape != (e, inter // g, h // 8):
+        raise ValueError("w2 scales/zeros shapes do not match group size")
+    if topk_weights.shape != (t, topk):
+        raise ValueError("topk_weights / topk_ids shape mismatch")
+    if global_num_experts not in (-1, e) and expert_map is None:
+        raise ValueError("global_num_experts differs from the stacked expert count")
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if t == 0:
+        return out
+    lib = _lib.load()
+    n_global = e if global_num_experts == -1 else global_num_experts
+    block = lib.awq_b200_moe_block_size(t, topk, n_global)
+    sorted_ids, expert_ids, num_post = moe_align_block_size(
+        topk_ids, block, n_global, expert_map, ignore_invalid_experts=True)
+    need = lib.awq_b200_moe_workspace_bytes(t, topk, n_global, h, inter)
+    ws = _workspace(hidden_states.device, need)
+    rc = lib.awq_b200_moe_experts(
+        hidden_states.data_ptr(), w13_q.data_ptr(), w13_s.data_ptr(), w13_z.data_ptr(),
+        w2_q.data_ptr(), w2_s.data_ptr(), w2_z.data_ptr(), topk_weights.data_ptr(),
+        sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), out.data_ptr(),
+        t, topk, e, h, inter, g, block, int(expert_map is not None), sorted_ids.numel(),
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+        _stream())
+    _lib.check("awq_b200_moe_experts", rc)
+    return out
+
+
+def fused_moe(hidden_states: torch.Tensor, w1, w2, gating_output: torch.Tensor, topk: int,
+              renormalize: bool, inplace: bool = False, group_size: int = 128) -> torch.Tensor:
+    """Routing followed by the experts: fused_topk then fused_experts (the historical
+    ``fused_moe`` entry point older call sites use)."""
+    w, ids, _ = fused_topk(hidden_states, gating_output, topk, renormalize)
+    return fused_experts(hidden_states, w1, w2, w, ids, inplace=inplace, group_size=group_size)

@@ -1,0 +1,212 @@
+// extern "C" boundary of libawq_b200.so: argument validation and kernel selection.
+// Declarations and their reference counterparts: include/awq_b200.h.
+#include "common.cuh"
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_device() {
+  static int cc_major[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return AWQ_B200_ERR_DEVICE;
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  if (cc_major[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+      return AWQ_B200_ERR_DEVICE;
+    cc_major[dev] = v;
+  }
+  return cc_major[dev] == 10 ? AWQ_B200_OK : AWQ_B200_ERR_DEVICE;
+}
+
+int check_awq_shape(int N, int K, int group) {
+  if (N <= 0 || K <= 0 || group <= 0) return AWQ_B200_ERR_SHAPE;
+  if (N % awq::kPack != 0) return AWQ_B200_ERR_SHAPE;
+  if (group % 8 != 0) return AWQ_B200_ERR_GROUP;
+  if (K % group != 0) return AWQ_B200_ERR_SHAPE;
+  return AWQ_B200_OK;
+}
+
+// Kernel choice for AWQ_B200_KERNEL_AUTO.
+int pick_gemm_kernel(int M, int N, int K, int group) {
+  if (M <= 32 && awq::gemm_stream_supported(M, N, K, group)) return AWQ_B200_KERNEL_STREAM;
+  if (awq::gemm_tc_supported(M, N, K, group)) return AWQ_B200_KERNEL_TCGEN05;
+  return AWQ_B200_KERNEL_GENERIC;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* awq_b200_strerror(int code) {
+  switch (code) {
+    case AWQ_B200_OK: return "ok";
+    case AWQ_B200_ERR_NULL: return "a required pointer is NULL";
+    case AWQ_B200_ERR_SHAPE: return "bad shape: size not positive or divisibility rule violated";
+    case AWQ_B200_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case AWQ_B200_ERR_GROUP: return "unsupported quantisation group size";
+    case AWQ_B200_ERR_WORKSPACE: return "workspace missing or too small";
+    case AWQ_B200_ERR_LAUNCH: return "CUDA launch failed";
+    case AWQ_B200_ERR_DEVICE: return "current device is not an sm_100 GPU";
+    case AWQ_B200_ERR_DRIVER: return "CUDA driver entry point unavailable";
+    case AWQ_B200_ERR_LIMIT: return "size exceeds a built-in capacity";
+    default: return "unknown error code";
+  }
+}
+
+const char* awq_b200_version(void) { return "0.1"; }
+
+int awq_b200_dequantize(const void* qweight, const void* scales, const void* qzeros, void* out,
+                        int K, int N, int group, void* stream) {
+  if (!qweight || !scales || !qzeros || !out) return AWQ_B200_ERR_NULL;
+  if (int rc = check_awq_shape(N, K, group)) return rc;
+  if (!aligned16(scales) || !aligned16(out) || !aligned16(qweight) || !aligned16(qzeros))
+    return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  return awq::launch_dequantize(static_cast<const uint32_t*>(qweight),
+                                static_cast<const __half*>(scales),
+                                static_cast<const uint32_t*>(qzeros), static_cast<__half*>(out), K,
+                                N, group, static_cast<cudaStream_t>(stream));
+}
+
+size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel) {
+  if (M <= 0 || check_awq_shape(N, K, group) != AWQ_B200_OK) return 0;
+  if (kernel == AWQ_B200_KERNEL_AUTO) kernel = pick_gemm_kernel(M, N, K, group);
+  if (kernel == AWQ_B200_KERNEL_TCGEN05) return awq::gemm_tc_workspace_bytes(M, N, K, group);
+  return 0;
+}
+
+int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const void* qzeros,
+                  const void* bias, void* out, int M, int N, int K, int group, int kernel,
+                  void* workspace, size_t workspace_bytes, void* stream) {
+  if (M == 0) return AWQ_B200_OK;
+  if (M < 0) return AWQ_B200_ERR_SHAPE;
+  if (!x || !qweight || !scales || !qzeros || !out) return AWQ_B200_ERR_NULL;
+  if (int rc = check_awq_shape(N, K, group)) return rc;
+  if (K % 8 != 0) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(scales) || !aligned16(qzeros) ||
+      !aligned16(out) || (bias && !aligned16(bias)))
+    return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  if (kernel == AWQ_B200_KERNEL_AUTO) kernel = pick_gemm_kernel(M, N, K, group);
+
+  const __half* xh = static_cast<const __half*>(x);
+  const uint32_t* qw = static_cast<const uint32_t*>(qweight);
+  const __half* sc = static_cast<const __half*>(scales);
+  const uint32_t* qz = static_cast<const uint32_t*>(qzeros);
+  const __half* bh = static_cast<const __half*>(bias);
+  __half* oh = static_cast<__half*>(out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  switch (kernel) {
+    case AWQ_B200_KERNEL_GENERIC:
+      return awq::launch_gemm_generic(xh, qw, sc, qz, bh, oh, M, N, K, group, st);
+    case AWQ_B200_KERNEL_STREAM:
+    case AWQ_B200_KERNEL_STREAM_EXACT:
+      if (!awq::gemm_stream_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+      return awq::launch_gemm_stream(xh, qw, sc, qz, bh, oh, M, N, K, group,
+                                     kernel == AWQ_B200_KERNEL_STREAM_EXACT, st);
+    case AWQ_B200_KERNEL_TCGEN05: {
+      if (!awq::gemm_tc_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+      const size_t need = awq::gemm_tc_workspace_bytes(M, N, K, group);
+      if (need > 0) {
+        if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
+        if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AWQ_B200_ERR_ALIGN;
+      }
+      return awq::launch_gemm_tc(xh, qw, sc, qz, bh, oh, M, N, K, group, workspace,
+                                 workspace_bytes, st);
+    }
+    default:
+      return AWQ_B200_ERR_SHAPE;
+  }
+}
+
+int awq_b200_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
+                          int renormalize, float* topk_weights, int32_t* topk_ids,
+                          int32_t* token_expert_indices, void* stream) {
+  if (T == 0) return AWQ_B200_OK;
+  if (!gating || !topk_weights || !topk_ids) return AWQ_B200_ERR_NULL;
+  if (T < 0 || E <= 0 || topk <= 0 || topk > E) return AWQ_B200_ERR_SHAPE;
+  if (gating_dtype != 0 && gating_dtype != 1) return AWQ_B200_ERR_SHAPE;
+  if (E > 1024 || topk > 32) return AWQ_B200_ERR_LIMIT;
+  if (int rc = check_device()) return rc;
+  return awq::launch_topk_softmax(gating, gating_dtype, T, E, topk, renormalize, topk_weights,
+                                  topk_ids, token_expert_indices,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int64_t awq_b200_moe_sorted_capacity(int64_t numel, int E, int block) {
+  if (numel < 0 || E <= 0 || block <= 0) return 0;
+  int64_t cap = numel + (int64_t)E * (block - 1);
+  if (numel < E) cap = numel * block < cap ? numel * block : cap;
+  return cap;
+}
+
+int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int E, int block,
+                                  const int32_t* expert_map, int32_t* sorted_ids,
+                                  int64_t sorted_capacity, int32_t* expert_ids,
+                                  int32_t* num_post_pad, void* stream) {
+  if (!sorted_ids || !expert_ids || !num_post_pad) return AWQ_B200_ERR_NULL;
+  if (T < 0 || topk <= 0 || E <= 0 || block <= 0) return AWQ_B200_ERR_SHAPE;
+  if (T > 0 && !topk_ids) return AWQ_B200_ERR_NULL;
+  const int64_t numel = (int64_t)T * topk;
+  if (E > 1024 || numel > (1 << 24)) return AWQ_B200_ERR_LIMIT;
+  if (sorted_capacity < awq_b200_moe_sorted_capacity(numel, E, block))
+    return AWQ_B200_ERR_WORKSPACE;
+  if (int rc = check_device()) return rc;
+  return awq::launch_moe_align(topk_ids, (int)numel, E, block, expert_map, sorted_ids,
+                               sorted_capacity, expert_ids, num_post_pad,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int awq_b200_moe_block_size(int T, int topk, int E) { return awq::moe_block_size(T, topk, E); }
+
+size_t awq_b200_moe_workspace_bytes(int T, int topk, int E, int H, int I) {
+  return awq::moe_workspace_bytes(T, topk, E, H, I);
+}
+
+int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, const void* w13_z,
+                         const void* w2_q, const void* w2_s, const void* w2_z,
+                         const float* topk_weights, const int32_t* sorted_ids,
+                         const int32_t* expert_ids, const int32_t* num_post_pad, void* out,
+                         int T, int topk, int E, int H, int I, int group, int block,
+                         int expert_parallel, int64_t sorted_capacity, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  if (T == 0) return AWQ_B200_OK;
+  if (!x || !w13_q || !w13_s || !w13_z || !w2_q || !w2_s || !w2_z || !topk_weights ||
+      !sorted_ids || !expert_ids || !num_post_pad || !out)
+    return AWQ_B200_ERR_NULL;
+  if (T < 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0 || block <= 0) return AWQ_B200_ERR_SHAPE;
+  if (group != 128 && group != 64 && group != 32) return AWQ_B200_ERR_GROUP;
+  if (!awq::moe_supported(H, I, group, block)) return AWQ_B200_ERR_SHAPE;
+  if ((int64_t)T * topk > (1 << 24)) return AWQ_B200_ERR_LIMIT;
+  if ((sorted_capacity + block - 1) / block > 65535) return AWQ_B200_ERR_LIMIT;
+  if (sorted_capacity < awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block))
+    return AWQ_B200_ERR_WORKSPACE;
+  if (!aligned16(x) || !aligned16(w13_q) || !aligned16(w13_s) || !aligned16(w13_z) ||
+      !aligned16(w2_q) || !aligned16(w2_s) || !aligned16(w2_z) || !aligned16(out))
+    return AWQ_B200_ERR_ALIGN;
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  awq::MoeArgs a{static_cast<const __half*>(x),
+                 static_cast<const uint32_t*>(w13_q),
+                 static_cast<const __half*>(w13_s),
+                 static_cast<const uint32_t*>(w13_z),
+                 static_cast<const uint32_t*>(w2_q),
+                 static_cast<const __half*>(w2_s),
+                 static_cast<const uint32_t*>(w2_z),
+                 topk_weights,
+                 sorted_ids,
+                 expert_ids,
+                 num_post_pad,
+                 static_cast<__half*>(out),
+                 T, topk, E, H, I, group, block,
+                 sorted_capacity,
+                 expert_parallel};
+  return awq::launch_moe_experts(a, workspace, workspace_bytes,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

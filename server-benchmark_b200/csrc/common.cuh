@@ -1,0 +1,147 @@
+// Shared device/host helpers for the AWQ W4A16 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/awq_b200.h"
+
+namespace awq {
+
+constexpr int kPack = 8;  // int4 values per int32 word
+
+// ---------------------------------------------------------------------------------------
+// AWQ nibble order.  Nibble p (LSB first) of a word holds column [0,2,4,6,1,3,5,7][p], so
+// for p in 0..3 nibble p is column 2p and nibble p+4 is column 2p+1: the two columns of an
+// adjacent pair sit exactly 16 bits apart.  (w >> 4p) & 0x000F000F therefore yields columns
+// (2p, 2p+1) in the low/high half of one register.
+// ---------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & b) | c
+  return r;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+__device__ __forceinline__ __half2 as_half2(uint32_t v) {
+  return *reinterpret_cast<__half2*>(&v);
+}
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// One packed word -> 4 registers; register p holds the fp16 values 1024 + q of columns
+// (2p, 2p+1).  1024 + q is exact in fp16 (0x6400 | q).
+__device__ __forceinline__ void unpack_word_magic(uint32_t w, uint32_t (&r)[4]) {
+  constexpr uint32_t kMask = 0x000F000Fu, kMagic = 0x64006400u;
+  r[0] = lop3_and_or(w, kMask, kMagic);
+  r[1] = lop3_and_or(w >> 4, kMask, kMagic);
+  r[2] = lop3_and_or(w >> 8, kMask, kMagic);
+  r[3] = lop3_and_or(w >> 12, kMask, kMagic);
+}
+
+// (q - z) * s in fp16 for the 8 columns of one word: the difference is exact, the product is
+// rounded once.  zmagic[p] = 1024 + z of columns (2p, 2p+1); s2[p] the matching scales.
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, const uint32_t (&zmagic)[4],
+                                              const __half2 (&s2)[4]) {
+  uint32_t q[4];
+  unpack_word_magic(w, q);
+  uint4 o;
+  o.x = as_u32(__hmul2(__hsub2(as_half2(q[0]), as_half2(zmagic[0])), s2[0]));
+  o.y = as_u32(__hmul2(__hsub2(as_half2(q[1]), as_half2(zmagic[1])), s2[1]));
+  o.z = as_u32(__hmul2(__hsub2(as_half2(q[2]), as_half2(zmagic[2])), s2[2]));
+  o.w = as_u32(__hmul2(__hsub2(as_half2(q[3]), as_half2(zmagic[3])), s2[3]));
+  return o;
+}
+
+// Integer nibble of column j (0..7) of a packed word.
+__device__ __forceinline__ int nibble_of_col(uint32_t w, int j) {
+  return (w >> (4 * ((j >> 1) + 4 * (j & 1)))) & 0xF;
+}
+
+// ---------------------------------------------------------------------------------------
+// cp.async (16-byte, L2-only) with zero fill when `valid` is false.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+// mma.sync m16n8k16, fp16 inputs, fp32 accumulate: d = a * b + c.
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1, const float (&c)[4]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]),
+        "f"(c[2]), "f"(c[3]));
+}
+
+// ---------------------------------------------------------------------------------------
+// Host-side entry points of the individual kernels (defined in the .cu files).
+// ---------------------------------------------------------------------------------------
+int sm_count();  // SMs of the current device (cached)
+
+int launch_dequantize(const uint32_t* qweight, const __half* scales, const uint32_t* qzeros,
+                      __half* out, int K, int N, int group, cudaStream_t stream);
+
+int launch_gemm_generic(const __half* x, const uint32_t* qweight, const __half* scales,
+                        const uint32_t* qzeros, const __half* bias, __half* out, int M, int N,
+                        int K, int group, cudaStream_t stream);
+
+bool gemm_stream_supported(int M, int N, int K, int group);
+int launch_gemm_stream(const __half* x, const uint32_t* qweight, const __half* scales,
+                       const uint32_t* qzeros, const __half* bias, __half* out, int M, int N,
+                       int K, int group, bool exact, cudaStream_t stream);
+
+bool gemm_tc_supported(int M, int N, int K, int group);
+size_t gemm_tc_workspace_bytes(int M, int N, int K, int group);
+int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scales,
+                   const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
+                   int group, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
+int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
+                        int renormalize, float* topk_weights, int32_t* topk_ids,
+                        int32_t* token_expert_indices, cudaStream_t stream);
+int launch_moe_align(const int32_t* topk_ids, int numel, int E, int block,
+                     const int32_t* expert_map, int32_t* sorted_ids, int64_t sorted_capacity,
+                     int32_t* expert_ids, int32_t* num_post_pad, cudaStream_t stream);
+
+struct MoeArgs {
+  const __half* x;
+  const uint32_t* w13_q;
+  const __half* w13_s;
+  const uint32_t* w13_z;
+  const uint32_t* w2_q;
+  const __half* w2_s;
+  const uint32_t* w2_z;
+  const float* topk_weights;
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  __half* out;
+  int T, topk, E, H, I, group, block;
+  int64_t sorted_capacity;
+  int expert_parallel;
+};
+bool moe_supported(int H, int I, int group, int block);
+size_t moe_workspace_bytes(int T, int topk, int E, int H, int I);
+int moe_block_size(int T, int topk, int E);
+int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream);
+
+}  // namespace awq

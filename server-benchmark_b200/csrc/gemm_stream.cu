@@ -1,0 +1,183 @@
+// Small-M AWQ GEMM (decode GEMV / small batches, M <= 32): weight streaming at HBM speed.
+//
+// y[M, N] = x[M, K] @ ((q - z) * s).  A CTA owns a slab of 256 output columns and a contiguous
+// range of K (see stream_core.cuh for the tile mainloop).  The CTAs that share a slab form a
+// thread-block cluster along K (cluster size S <= 8); their fp32 partial tiles are combined
+// through distributed shared memory in rank order, so split-K needs no global scratch and no
+// atomics, and the result is bit-reproducible.
+#include <cooperative_groups.h>
+
+#include "stream_core.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace awq {
+
+namespace {
+
+using namespace stream;
+
+struct StreamParams {
+  const __half* x;
+  const uint32_t* qweight;
+  const __half* scales;
+  const uint32_t* qzeros;
+  const __half* bias;
+  __half* out;
+  int M, N, K, group;
+};
+
+template <int MT, bool EXACT>
+__global__ void __launch_bounds__(kThreads, 2) gemm_stream_kernel(const StreamParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int S = (int)cluster.num_blocks();
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2;
+  const int words = p.N / kPack;
+  const int word0 = blockIdx.y * (kBN / kPack);
+  const int KT = p.K / kBK;
+  const int st_begin = (int)(((long long)rank * KT) / S);
+  const int st_end = (int)(((long long)(rank + 1) * KT) / S);
+
+  TileSrc<MT> src;
+  {
+    const int wc = word0 + (tid & 7) * 4;
+    src.wvalid = wc < words;
+    src.wsrc = p.qweight + (src.wvalid ? wc : 0);
+    src.wrow_words = (size_t)words;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      const int row = (tid >> 4) + 8 * j;
+      src.xvalid[j] = row < p.M;
+      src.xsrc[j] = p.x + (size_t)(src.xvalid[j] ? row : 0) * p.K + (tid & 15) * 8;
+    }
+    const int wcol = word0 + 8 * warp + g;
+    const int wcol_ld = wcol < words ? wcol : words - 1;  // clamped past the N edge
+    src.zsrc = p.qzeros + wcol_ld;
+    src.ssrc = reinterpret_cast<const uint4*>(p.scales) + wcol_ld;
+    src.zpitch = (size_t)words;
+    src.spitch = (size_t)words;
+  }
+
+  float tot[MT][4][4];
+  mainloop<MT, EXACT>(src, smem_u32(smem), st_begin, st_end - st_begin, p.group, p.K / p.group,
+                      tot);
+
+  // ---- cluster reduction through distributed shared memory ----
+  float* red = reinterpret_cast<float*>(smem);
+  store_tile<MT>(red, tot);
+  cluster.sync();
+  {
+    constexpr int kUnits = kBN / 8;  // 8-column units in the slab
+    const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
+    const int nun = uend - ubeg;
+    const int n_slab = blockIdx.y * kBN;
+    for (int idx = tid; idx < nun * MT * 8; idx += kThreads) {
+      const int u = ubeg + idx % nun, m = idx / nun;
+      const int n = n_slab + u * 8;
+      if (m >= p.M || n >= p.N) continue;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      for (int q = 0; q < S; ++q) {
+        const float* peer = cluster.map_shared_rank(red, q) + m * kRedPitch + u * 8;
+        const float4 a = *reinterpret_cast<const float4*>(peer);
+        const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
+      if (p.bias != nullptr) {
+        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+        const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += __half2float(bh[j]);
+      }
+      __align__(16) __half o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(v[j]);
+      *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+  cluster.sync();  // keep this CTA's shared memory alive until every peer has read it
+}
+
+template <int MT, bool EXACT>
+int launch_variant(const StreamParams& p, cudaStream_t stream) {
+  constexpr int smem = Cfg<MT>::kSmemBytes;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  if (!attr_done[dev]) {
+    if (cudaFuncSetAttribute(gemm_stream_kernel<MT, EXACT>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+    attr_done[dev] = true;
+  }
+  const int slabs = (p.N + kBN - 1) / kBN;
+  const int KT = p.K / kBK;
+  const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
+  int S = (ctas_per_sm * sm_count()) / slabs;
+  S = S < 1 ? 1 : (S > 8 ? 8 : S);
+  if (S > KT) S = KT;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S, slabs, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_stream_kernel<MT, EXACT>, p) != cudaSuccess) {
+    cudaGetLastError();
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
+}
+
+template <bool EXACT>
+int launch_by_m(const StreamParams& p, cudaStream_t stream) {
+  if (p.M <= 8) return launch_variant<1, EXACT>(p, stream);
+  if (p.M <= 16) return launch_variant<2, EXACT>(p, stream);
+  return launch_variant<4, EXACT>(p, stream);
+}
+
+}  // namespace
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      v = 148;
+    cached[dev] = v;
+  }
+  return cached[dev];
+}
+
+bool gemm_stream_supported(int M, int N, int K, int group) {
+  // 16-byte cp.async needs 16-byte-aligned weight rows (N % 32) and x rows (K % 128 covers it);
+  // a stage is 128 rows and a group must tile it in whole 16-row steps.
+  return M >= 1 && M <= 32 && N % 32 == 0 && K % kBK == 0 &&
+         (group == 128 || group == 64 || group == 32);
+}
+
+int launch_gemm_stream(const __half* x, const uint32_t* qweight, const __half* scales,
+                       const uint32_t* qzeros, const __half* bias, __half* out, int M, int N,
+                       int K, int group, bool exact, cudaStream_t stream) {
+  if (!gemm_stream_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+  StreamParams p{x, qweight, scales, qzeros, bias, out, M, N, K, group};
+  return exact ? launch_by_m<true>(p, stream) : launch_by_m<false>(p, stream);
+}
+
+}  // namespace awq

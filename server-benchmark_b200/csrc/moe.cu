@@ -1,0 +1,519 @@
+// AWQ fused-MoE layer: router, token -> expert permutation, grouped expert GEMMs.
+//
+//   topk_softmax_kernel   one warp per token: softmax over E logits, k rounds of warp arg-max
+//                         (ties -> lower expert id), optional renormalisation.
+//   moe_align_kernel      stable counting sort of the T*k (token, slot) pairs by expert with
+//                         every expert's run padded to the GEMM row block; one CTA per 8 experts,
+//                         each CTA rebuilds the (cheap) histogram and prefix itself so a single
+//                         launch suffices; within an expert a warp ranks pairs with ballots, in
+//                         ascending flat index, hence a deterministic order.
+//   moe_gemm1_kernel      per (row block, 128 gate + 128 up columns): x rows gathered through the
+//                         permutation, expert weights streamed (stream_core.cuh), epilogue
+//                         silu(gate) * up -> fp16 activation in permuted row order.
+//   moe_gemm2_kernel      per (row block, 256 hidden columns): activation rows x down weights,
+//                         epilogue times routed weight -> fp16 row of the (token, slot) pair.
+//   moe_sum_kernel        out[t] = sum over the k slots of token t, fp32 accumulation.
+// The GEMMs split K across a thread-block cluster and reduce through distributed shared
+// memory, exactly like the dense small-M kernel.
+#include <cooperative_groups.h>
+
+#include "stream_core.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace awq {
+
+namespace {
+
+using namespace stream;
+
+// ------------------------------------------------------------------------------- router
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+constexpr int kTopkWarps = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kTopkWarps * 32)
+topk_softmax_kernel(const T* __restrict__ gating, int tokens, int E, int topk, int renorm,
+                    float* __restrict__ out_w, int32_t* __restrict__ out_ids,
+                    int32_t* __restrict__ out_tok) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x * kTopkWarps + warp;
+  if (token >= tokens) return;
+  const T* row = gating + (size_t)token * E;
+  const float kNegInf = -__int_as_float(0x7f800000);
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? to_f32<T>(row[e]) : kNegInf;
+  }
+  float mx = kNegInf;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) sum += (lane + 32 * i < E) ? __expf(v[i] - mx) : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+
+  float my_w = 0.f;
+  int my_id = 0;
+  uint32_t taken = 0;  // bit i: entry lane + 32 i already selected
+  for (int j = 0; j < topk; ++j) {
+    float bv = kNegInf;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int e = lane + 32 * i;
+      // ascending e: a strict comparison keeps the lower id on ties
+      if (e < E && !((taken >> i) & 1u) && (bi == 0x7fffffff || v[i] > bv)) {
+        bv = v[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == j) {
+      my_w = __expf(bv - mx) * inv;
+      my_id = bi;
+    }
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+  }
+  if (renorm) {
+    float s = lane < topk ? my_w : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    my_w = my_w / s;
+  }
+  if (lane < topk) {
+    out_w[(size_t)token * topk + lane] = my_w;
+    out_ids[(size_t)token * topk + lane] = my_id;
+    if (out_tok != nullptr) out_tok[(size_t)token * topk + lane] = lane * tokens + token;
+  }
+}
+
+// ------------------------------------------------------------------------------- permutation
+
+constexpr int kAlignThreads = 256;
+constexpr int kAlignExpertsPerCta = kAlignThreads / 32;
+constexpr int kMaxExperts = 1024;
+
+__global__ void __launch_bounds__(kAlignThreads)
+moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
+                 const int32_t* __restrict__ expert_map, int32_t* __restrict__ sorted_ids,
+                 int64_t capacity, int32_t* __restrict__ expert_ids,
+                 int32_t* __restrict__ num_post_pad) {
+  __shared__ int hist[kMaxExperts];
+  __shared__ int offs[kMaxExperts + 1];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < E; e += kAlignThreads) hist[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < numel; i += kAlignThreads) {
+    const int id = ids[i];
+    if (id >= 0 && id < E && (expert_map == nullptr || expert_map[id] >= 0))
+      atomicAdd(&hist[id], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = run;
+      run += ((hist[e] + block - 1) / block) * block;
+    }
+    offs[E] = run;
+  }
+  __syncthreads();
+  const int total = offs[E];
+
+  const int e = blockIdx.x * kAlignExpertsPerCta + warp;
+  if (e < E && hist[e] > 0) {
+    const int base = offs[e];
+    const int padded = offs[e + 1] - base;
+    int cnt = 0;
+    for (int i0 = 0; i0 < numel; i0 += 32) {
+      const int i = i0 + lane;
+      const bool m = i < numel && ids[i] == e;
+      const unsigned b = __ballot_sync(0xffffffffu, m);
+      if (m) sorted_ids[base + cnt + __popc(b & ((1u << lane) - 1u))] = i;
+      cnt += __popc(b);
+    }
+    for (int j = cnt + lane; j < padded; j += 32) sorted_ids[base + j] = numel;
+    const int local = expert_map == nullptr ? e : expert_map[e];
+    for (int bk = lane; bk < padded / block; bk += 32) expert_ids[base / block + bk] = local;
+  }
+  if (blockIdx.x == 0) {
+    if (tid == 0) num_post_pad[0] = total;
+    for (int64_t j = total + tid; j < capacity; j += kAlignThreads) sorted_ids[j] = numel;
+    const int64_t nblk = (capacity + block - 1) / block;
+    for (int64_t bk = total / block + tid; bk < nblk; bk += kAlignThreads) expert_ids[bk] = -1;
+  }
+}
+
+// ------------------------------------------------------------------------------- grouped GEMMs
+
+constexpr int kMoeMT = 2;          // 16-row blocks
+constexpr bool kMoeExact = false;  // conversion used by the expert GEMMs (see stream_core.cuh)
+
+struct Gemm1Params {
+  const __half* x;           // [T, H]
+  const uint32_t* w13_q;     // [E, H, 2I/8]
+  const __half* w13_s;       // [E, H/G, 2I]
+  const uint32_t* w13_z;     // [E, H/G, 2I/8]
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  __half* act;               // [capacity, I] in permuted row order
+  int numel, topk, H, I, group;
+};
+
+__global__ void __launch_bounds__(kThreads, 2) moe_gemm1_kernel(const Gemm1Params p) {
+  constexpr int MT = kMoeMT;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int S = (int)cluster.num_blocks();
+  const int blk = blockIdx.z;
+  const int pos0 = blk * (8 * MT);
+  // uniform over the cluster: nobody reaches a cluster barrier if the block is unused
+  if (pos0 >= p.num_post_pad[0]) return;
+  const int e = p.expert_ids[blk];
+  if (e < 0) return;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2;
+  const int words = 2 * p.I / kPack;  // weight row pitch
+  const int iw = p.I / kPack;         // words of the gate half
+  const int seg0 = blockIdx.y * 16;   // first word of this slab inside the gate (and up) half
+  const int groups = p.H / p.group;
+  const uint32_t* wq = p.w13_q + (size_t)e * p.H * words;
+  const uint32_t* wz = p.w13_z + (size_t)e * groups * words;
+  const __half* ws = p.w13_s + (size_t)e * groups * (2 * p.I);
+
+  TileSrc<MT> src;
+  {
+    const int c = tid & 7;
+    const int in_seg = seg0 + (c & 3) * 4;       // word inside the half
+    src.wvalid = in_seg < iw;
+    const int wc = (c < 4 ? 0 : iw) + (src.wvalid ? in_seg : 0);
+    src.wsrc = wq + wc;
+    src.wrow_words = (size_t)words;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      const int row = (tid >> 4) + 8 * j;
+      const int fid = p.sorted_ids[pos0 + row];
+      src.xvalid[j] = fid < p.numel;
+      const int token = src.xvalid[j] ? fid / p.topk : 0;
+      src.xsrc[j] = p.x + (size_t)token * p.H + (tid & 15) * 8;
+    }
+    int in_seg_c = seg0 + 8 * (warp & 1) + g;
+    if (in_seg_c >= iw) in_seg_c = iw - 1;
+    const int wcol = (warp < 2 ? 0 : iw) + in_seg_c;
+    src.zsrc = wz + wcol;
+    src.ssrc = reinterpret_cast<const uint4*>(ws) + wcol;
+    src.zpitch = (size_t)words;
+    src.spitch = (size_t)words;
+  }
+  const int KT = p.H / kBK;
+  const int st_begin = (int)(((long long)rank * KT) / S);
+  const int st_end = (int)(((long long)(rank + 1) * KT) / S);
+
+  float tot[MT][4][4];
+  mainloop<MT, kMoeExact>(src, smem_u32(smem), st_begin, st_end - st_begin, p.group, groups, tot);
+
+  float* red = reinterpret_cast<float*>(smem);
+  store_tile<MT>(red, tot);
+  cluster.sync();
+  {
+    constexpr int kUnits = 16;  // 8-column units of the 128 activation columns
+    const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
+    const int nun = uend - ubeg;
+    for (int idx = tid; idx < nun * MT * 8; idx += kThreads) {
+      const int u = ubeg + idx % nun, m = idx / nun;
+      const int col = blockIdx.y * 128 + u * 8;
+      if (col >= p.I) continue;
+      float gt[8], up[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gt[j] = up[j] = 0.f;
+      for (int q = 0; q < S; ++q) {
+        const float* peer = cluster.map_shared_rank(red, q) + m * kRedPitch + u * 8;
+        const float4 a = *reinterpret_cast<const float4*>(peer);
+        const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+        const float4 c = *reinterpret_cast<const float4*>(peer + 128);
+        const float4 d = *reinterpret_cast<const float4*>(peer + 132);
+        gt[0] += a.x; gt[1] += a.y; gt[2] += a.z; gt[3] += a.w;
+        gt[4] += b.x; gt[5] += b.y; gt[6] += b.z; gt[7] += b.w;
+        up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w;
+        up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
+      }
+      __align__(16) __half o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(gt[j] / (1.f + __expf(-gt[j])) * up[j]);
+      *reinterpret_cast<uint4*>(p.act + (size_t)(pos0 + m) * p.I + col) =
+          *reinterpret_cast<uint4*>(o);
+    }
+  }
+  cluster.sync();
+}
+
+struct Gemm2Params {
+  const __half* act;         // [capacity, I]
+  const uint32_t* w2_q;      // [E, I, H/8]
+  const __half* w2_s;        // [E, I/G, H]
+  const uint32_t* w2_z;      // [E, I/G, H/8]
+  const float* topk_weights; // [T * topk]
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  __half* pair_out;          // [T * topk, H]
+  int numel, H, I, group;
+};
+
+__global__ void __launch_bounds__(kThreads, 2) moe_gemm2_kernel(const Gemm2Params p) {
+  constexpr int MT = kMoeMT;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ int s_fid[8 * MT];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int S = (int)cluster.num_blocks();
+  const int blk = blockIdx.z;
+  const int pos0 = blk * (8 * MT);
+  if (pos0 >= p.num_post_pad[0]) return;
+  const int e = p.expert_ids[blk];
+  if (e < 0) return;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2;
+  const int words = p.H / kPack;
+  const int word0 = blockIdx.y * (kBN / kPack);
+  const int groups = p.I / p.group;
+  const uint32_t* wq = p.w2_q + (size_t)e * p.I * words;
+  const uint32_t* wz = p.w2_z + (size_t)e * groups * words;
+  const __half* ws = p.w2_s + (size_t)e * groups * p.H;
+  if (tid < 8 * MT) s_fid[tid] = p.sorted_ids[pos0 + tid];
+
+  TileSrc<MT> src;
+  {
+    const int wc = word0 + (tid & 7) * 4;
+    src.wvalid = wc < words;
+    src.wsrc = wq + (src.wvalid ? wc : 0);
+    src.wrow_words = (size_t)words;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      const int row = (tid >> 4) + 8 * j;
+      src.xvalid[j] = p.sorted_ids[pos0 + row] < p.numel;
+      src.xsrc[j] = p.act + (size_t)(pos0 + row) * p.I + (tid & 15) * 8;
+    }
+    const int wcol = word0 + 8 * warp + g;
+    const int wcol_ld = wcol < words ? wcol : words - 1;
+    src.zsrc = wz + wcol_ld;
+    src.ssrc = reinterpret_cast<const uint4*>(ws) + wcol_ld;
+    src.zpitch = (size_t)words;
+    src.spitch = (size_t)words;
+  }
+  const int KT = p.I / kBK;
+  const int st_begin = (int)(((long long)rank * KT) / S);
+  const int st_end = (int)(((long long)(rank + 1) * KT) / S);
+
+  float tot[MT][4][4];
+  mainloop<MT, kMoeExact>(src, smem_u32(smem), st_begin, st_end - st_begin, p.group, groups, tot);
+
+  float* red = reinterpret_cast<float*>(smem);
+  store_tile<MT>(red, tot);
+  cluster.sync();
+  {
+    constexpr int kUnits = kBN / 8;
+    const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
+    const int nun = uend - ubeg;
+    for (int idx = tid; idx < nun * MT * 8; idx += kThreads) {
+      const int u = ubeg + idx % nun, m = idx / nun;
+      const int n = blockIdx.y * kBN + u * 8;
+      const int fid = s_fid[m];
+      if (fid >= p.numel || n >= p.H) continue;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      for (int q = 0; q < S; ++q) {
+        const float* peer = cluster.map_shared_rank(red, q) + m * kRedPitch + u * 8;
+        const float4 a = *reinterpret_cast<const float4*>(peer);
+        const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
+      const float rw = __ldg(p.topk_weights + fid);
+      __align__(16) __half o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(v[j] * rw);
+      *reinterpret_cast<uint4*>(p.pair_out + (size_t)fid * p.H + n) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+  cluster.sync();
+}
+
+// out[t, h] = sum_slot pair_out[t * topk + slot, h]; one thread per 8 columns.
+__global__ void __launch_bounds__(256)
+moe_sum_kernel(const __half* __restrict__ pair_out, __half* __restrict__ out, int T, int topk,
+               int H) {
+  const int units = H / 8;
+  const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= (long long)T * units) return;
+  const int t = (int)(idx / units), u = (int)(idx % units);
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  for (int s = 0; s < topk; ++s) {
+    const uint4 r =
+        __ldg(reinterpret_cast<const uint4*>(pair_out + ((size_t)t * topk + s) * H) + u);
+    const __half* h = reinterpret_cast<const __half*>(&r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += __half2float(h[j]);
+  }
+  __align__(16) __half o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(v[j]);
+  *(reinterpret_cast<uint4*>(out + (size_t)t * H) + u) = *reinterpret_cast<uint4*>(o);
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int pick_cluster(int tiles, int KT) {
+  int S = tiles > 0 ? (2 * sm_count()) / tiles : 8;
+  S = S < 1 ? 1 : (S > 8 ? 8 : S);
+  return S > KT ? KT : S;
+}
+
+template <typename P>
+int launch_clustered(void (*kernel)(const P), const P& p, dim3 grid, int S, cudaStream_t stream) {
+  constexpr int smem = Cfg<kMoeMT>::kSmemBytes;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
+    cudaGetLastError();
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
+}
+
+}  // namespace
+
+int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
+                        int renormalize, float* topk_weights, int32_t* topk_ids,
+                        int32_t* token_expert_indices, cudaStream_t stream) {
+  const int grid = (T + kTopkWarps - 1) / kTopkWarps;
+  if (gating_dtype == 0)
+    topk_softmax_kernel<float><<<grid, kTopkWarps * 32, 0, stream>>>(
+        static_cast<const float*>(gating), T, E, topk, renormalize, topk_weights, topk_ids,
+        token_expert_indices);
+  else
+    topk_softmax_kernel<__half><<<grid, kTopkWarps * 32, 0, stream>>>(
+        static_cast<const __half*>(gating), T, E, topk, renormalize, topk_weights, topk_ids,
+        token_expert_indices);
+  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
+int launch_moe_align(const int32_t* topk_ids, int numel, int E, int block,
+                     const int32_t* expert_map, int32_t* sorted_ids, int64_t sorted_capacity,
+                     int32_t* expert_ids, int32_t* num_post_pad, cudaStream_t stream) {
+  const int grid = (E + kAlignExpertsPerCta - 1) / kAlignExpertsPerCta;
+  moe_align_kernel<<<grid, kAlignThreads, 0, stream>>>(topk_ids, numel, E, block, expert_map,
+                                                       sorted_ids, sorted_capacity, expert_ids,
+                                                       num_post_pad);
+  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
+int moe_block_size(int, int, int) { return 8 * kMoeMT; }
+
+bool moe_supported(int H, int I, int group, int block) {
+  // gate/up halves start on 16-byte boundaries (I % 32), stages are 128 rows of K
+  return block == 8 * kMoeMT && H % kBK == 0 && I % kBK == 0 && I % 32 == 0 && H % 32 == 0 &&
+         (group == 128 || group == 64 || group == 32);
+}
+
+size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
+  if (T <= 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0) return 0;
+  const int block = moe_block_size(T, topk, E);
+  const int64_t cap = awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block);
+  const int64_t rows = (cap + block - 1) / block * block;
+  return align_up((size_t)rows * I * sizeof(__half), 256) +
+         align_up((size_t)T * topk * H * sizeof(__half), 256);
+}
+
+int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream) {
+  const size_t need = moe_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
+  if (workspace == nullptr || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
+  const int numel = a.T * a.topk;
+  const int64_t rows = (a.sorted_capacity + a.block - 1) / a.block * a.block;
+  const int nblk = (int)(rows / a.block);
+  __half* act = static_cast<__half*>(workspace);
+  __half* pair_out = reinterpret_cast<__half*>(static_cast<uint8_t*>(workspace) +
+                                               align_up((size_t)rows * a.I * sizeof(__half), 256));
+
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  if (!attr_done[dev]) {
+    constexpr int smem = Cfg<kMoeMT>::kSmemBytes;
+    if (cudaFuncSetAttribute(moe_gemm1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess ||
+        cudaFuncSetAttribute(moe_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+    attr_done[dev] = true;
+  }
+  if (a.expert_parallel) {
+    // pairs routed to experts of other ranks are never written: they must read as zero
+    if (cudaMemsetAsync(pair_out, 0, (size_t)numel * a.H * sizeof(__half), stream) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+  }
+  {
+    Gemm1Params p{a.x, a.w13_q, a.w13_s, a.w13_z, a.sorted_ids, a.expert_ids, a.num_post_pad,
+                  act, numel, a.topk, a.H, a.I, a.group};
+    const int slabs = (a.I + 127) / 128;
+    const int S = pick_cluster(slabs * nblk, a.H / kBK);
+    if (int rc = launch_clustered(moe_gemm1_kernel, p, dim3(S, slabs, nblk), S, stream)) return rc;
+  }
+  {
+    Gemm2Params p{act, a.w2_q, a.w2_s, a.w2_z, a.topk_weights, a.sorted_ids, a.expert_ids,
+                  a.num_post_pad, pair_out, numel, a.H, a.I, a.group};
+    const int slabs = (a.H + kBN - 1) / kBN;
+    const int S = pick_cluster(slabs * nblk, a.I / kBK);
+    if (int rc = launch_clustered(moe_gemm2_kernel, p, dim3(S, slabs, nblk), S, stream)) return rc;
+  }
+  {
+    const long long work = (long long)a.T * (a.H / 8);
+    moe_sum_kernel<<<(unsigned)((work + 255) / 256), 256, 0, stream>>>(pair_out, a.out, a.T,
+                                                                       a.topk, a.H);
+    if (cudaGetLastError() != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
+}
+
+}  // namespace awq

@@ -1,0 +1,105 @@
+"""The C-ABI library loads and exports every symbol include/awq_b200.h declares; host-side
+validation paths that need no GPU return the documented codes."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "awq_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(awq_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for n in ["awq_b200_gemm", "awq_b200_dequantize", "awq_b200_topk_softmax",
+              "awq_b200_moe_align_block_size", "awq_b200_moe_experts", "awq_b200_strerror"]:
+        assert n in names
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    lib = ctypes.CDLL(built_library)
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in awq_b200.h but not exported"
+
+
+def test_python_prototypes_cover_the_header(built_library):
+    from awq_b200 import _lib
+    assert sorted(_lib.PROTOTYPES) == declared_symbols()
+    lib = _lib.load()
+    assert lib.awq_b200_version().decode() == "0.1"
+    assert _lib.strerror(0) == "ok"
+    assert "NULL" in _lib.strerror(-1)
+    assert "unknown" in _lib.strerror(-1234)
+
+
+def test_host_side_validation_without_gpu(built_library):
+    """Argument checks run before any CUDA call, so they are testable on a CPU-only box."""
+    from awq_b200 import _lib
+    lib = _lib.load()
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    p = (p + 255) & ~255
+    # NULL pointer
+    assert lib.awq_b200_gemm(None, p, p, p, None, p, 1, 8, 128, 128, 0, None, 0, None) == -1
+    # N not a multiple of 8
+    assert lib.awq_b200_gemm(p, p, p, p, None, p, 1, 12, 128, 128, 0, None, 0, None) == -2
+    # K not a multiple of the group
+    assert lib.awq_b200_gemm(p, p, p, p, None, p, 1, 8, 192, 128, 0, None, 0, None) == -2
+    # group not a multiple of 8
+    assert lib.awq_b200_dequantize(p, p, p, p, 100, 8, 100, None) == -4
+    # misaligned pointer
+    assert lib.awq_b200_gemm(p + 4, p, p, p, None, p, 1, 8, 128, 128, 0, None, 0, None) == -3
+    # M == 0 is a no-op
+    assert lib.awq_b200_gemm(None, None, None, None, None, None, 0, 8, 128, 128, 0, None, 0,
+                             None) == 0
+    # capacity formula (fused_moe/moe_align_block_size.py:74-80)
+    assert lib.awq_b200_moe_sorted_capacity(8, 128, 16) == 128
+    assert lib.awq_b200_moe_sorted_capacity(1024, 128, 16) == 1024 + 128 * 15
+    # router limits
+    assert lib.awq_b200_topk_softmax(p, 0, 4, 2048, 8, 1, p, p, p, None) == -9
+    assert lib.awq_b200_topk_softmax(p, 0, 4, 8, 9, 1, p, p, p, None) == -2
+    # sorted_ids too small
+    assert lib.awq_b200_moe_align_block_size(p, 4, 2, 8, 4, None, p, 3, p, p, None) == -5
+
+
+def test_ops_reject_cpu_tensors(built_library):
+    import torch
+    import awq_b200
+    q = torch.zeros(128, 1, dtype=torch.int32)
+    s = torch.zeros(1, 8, dtype=torch.float16)
+    x = torch.zeros(1, 128, dtype=torch.float16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        awq_b200.awq_gemm(x, q, s, q[:1], 8)
+    with pytest.raises(ValueError, match="no CPU path"):
+        awq_b200.awq_dequantize(q, s, q[:1], 0, 0, 0)
+
+
+def test_linear_method_weight_contract(built_library):
+    import torch
+    from awq_b200 import AWQConfig, AWQLinear, AWQLinearMethod
+    m = AWQLinearMethod(AWQConfig(group_size=128))
+    layer = AWQLinear()
+    m.create_weights(layer, 256, [64, 64], 256, 128, torch.float16, device="cpu")
+    assert layer.qweight.shape == (256, 16) and layer.qweight.dtype == torch.int32
+    assert layer.qzeros.shape == (2, 16) and layer.scales.shape == (2, 128)
+    with pytest.raises(ValueError, match="input size is not aligned"):
+        m.create_weights(AWQLinear(), 200, [64], 200, 64, torch.float16, device="cpu")
+    with pytest.raises(ValueError, match="output size is not aligned"):
+        m.create_weights(AWQLinear(), 256, [60], 256, 60, torch.float16, device="cpu")
+    with pytest.raises(ValueError):
+        AWQConfig(weight_bits=8)
+
+
+def test_missing_library_fails_loudly(monkeypatch, built_library):
+    from awq_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libawq_b200.so")
+    with pytest.raises(ImportError, match="no fallback"):
+        _lib.load()

@@ -1,0 +1,148 @@
+"""Parity of the router, the token->expert permutation and the fused expert GEMMs with the CPU
+oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import awq_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def A(built_library):
+    import awq_b200
+    assert torch.cuda.is_available()
+    return awq_b200
+
+
+@pytest.mark.parametrize("t,e,k,renorm,dtype", [
+    (1, 128, 8, True, torch.float32), (16, 128, 8, True, torch.float32),
+    (333, 128, 8, False, torch.float32), (7, 8, 2, True, torch.float16),
+    (5, 1000, 32, True, torch.float32), (4096, 128, 8, True, torch.float32),
+])
+def test_topk_softmax(A, t, e, k, renorm, dtype):
+    g = torch.randn(t, e, generator=torch.Generator().manual_seed(t + e)).to(dtype)
+    hs = torch.empty(t, 4, dtype=torch.float16, device="cuda")
+    w, ids, tok = A.fused_topk(hs, g.cuda(), k, renorm)
+    rw, rids, rtok = O.topk_softmax(g.float().numpy(), k, renorm)
+    assert np.array_equal(ids.cpu().numpy(), rids)          # indices bit-exact
+    assert np.array_equal(tok.cpu().numpy(), rtok)
+    assert np.allclose(w.cpu().numpy(), rw, rtol=2e-5, atol=1e-7)
+
+
+def test_topk_ties_pick_lower_id(A):
+    g = torch.zeros(3, 128)
+    g[1, 100] = 1.0
+    hs = torch.empty(3, 4, dtype=torch.float16, device="cuda")
+    _, ids, _ = A.fused_topk(hs, g.cuda(), 8, True)
+    assert ids[0].tolist() == list(range(8))
+    assert ids[1].tolist() == [100] + list(range(7))
+
+
+@pytest.mark.parametrize("t,k,e,blk", [
+    (1, 8, 128, 16), (16, 8, 128, 16), (128, 8, 128, 16), (1024, 8, 128, 16), (4096, 8, 128, 16),
+    (4, 3, 4, 4), (33, 2, 8, 4), (100, 1, 1000, 8), (64, 8, 128, 64),
+])
+def test_moe_align_bit_exact(A, t, k, e, blk):
+    rng = np.random.default_rng(t * 31 + e)
+    ids = np.stack([rng.permutation(e)[:k] for _ in range(t)]).astype(np.int32)
+    s, eid, post = A.moe_align_block_size(torch.from_numpy(ids).cuda(), blk, e)
+    rs, reid, rpost = O.moe_align_block_size(ids, blk, e)
+    assert np.array_equal(post.cpu().numpy(), rpost)
+    assert np.array_equal(s.cpu().numpy(), rs)
+    assert np.array_equal(eid.cpu().numpy(), reid)
+
+
+def test_moe_align_docstring_example(A, golden):
+    ids = torch.from_numpy(golden["align.topk_ids"]).cuda()
+    s, eid, post = A.moe_align_block_size(ids, 4, 4)
+    assert post.item() == 16
+    assert s[:16].cpu().tolist() == golden["align.sorted_ids"].tolist()
+    assert eid[:4].cpu().tolist() == [0, 1, 2, 3]
+
+
+def test_moe_align_expert_map(A):
+    rng = np.random.default_rng(9)
+    t, k, e, blk = 50, 4, 16, 8
+    ids = np.stack([rng.permutation(e)[:k] for _ in range(t)]).astype(np.int32)
+    emap = np.full(e, -1, dtype=np.int32)
+    emap[4:8] = np.arange(4)
+    s, eid, post = A.moe_align_block_size(torch.from_numpy(ids).cuda(), blk, e,
+                                          torch.from_numpy(emap).cuda(),
+                                          ignore_invalid_experts=True)
+    rs, reid, rpost = O.moe_align_block_size(ids, blk, e, emap)
+    assert np.array_equal(post.cpu().numpy(), rpost)
+    assert np.array_equal(s.cpu().numpy(), rs)
+    assert np.array_equal(eid.cpu().numpy(), reid)
+
+
+def test_moe_align_against_installed_vllm(A):
+    try:
+        from vllm.model_executor.layers.fused_moe.moe_align_block_size import (
+            moe_align_block_size as v_align)
+        import vllm._moe_C  # noqa: F401
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"vllm compiled ops unavailable: {e}")
+    rng = np.random.default_rng(4)
+    t, k, e, blk = 200, 8, 128, 16
+    ids = np.stack([rng.permutation(e)[:k] for _ in range(t)]).astype(np.int32)
+    idt = torch.from_numpy(ids).cuda()
+    s, eid, post = A.moe_align_block_size(idt, blk, e)
+    vs, veid, vpost = v_align(idt, blk, e)
+    assert post.item() == vpost.item()
+    nb = post.item() // blk
+    assert torch.equal(eid[:nb], veid[:nb])
+    a = s[:post.item()].reshape(nb, blk).sort(dim=1).values
+    b = vs[:post.item()].reshape(nb, blk).sort(dim=1).values
+    assert torch.equal(a, b)   # same per-block sets; within-block order is ours (ascending)
+
+
+def _moe_case(e, h, i, t, k, seed):
+    from awq_b200 import synth
+    w1, w2 = synth.moe_layer_tensors(e, h, i, 128, seed=seed)
+    x = synth.activations(t, h, seed=seed + 1)
+    logits = synth.gating_logits(t, e, seed=seed + 2)
+    return w1, w2, x, logits
+
+
+@pytest.mark.parametrize("e,h,i,t,k", [
+    (4, 256, 128, 5, 2), (8, 512, 256, 1, 2), (16, 2048, 768, 16, 8), (128, 2048, 768, 1, 8),
+    (128, 2048, 768, 40, 8), (8, 256, 128, 300, 2),
+])
+def test_fused_experts_vs_oracle(A, e, h, i, t, k):
+    w1, w2, x, logits = _moe_case(e, h, i, t, k, seed=e + t)
+    w, ids, _ = O.topk_softmax(logits.numpy(), k, True)
+    ref = O.fused_experts_fp32(x.numpy(), *[a.numpy() for a in w1], *[a.numpy() for a in w2],
+                               w, ids)
+    w1d = tuple(a.cuda() for a in w1)
+    w2d = tuple(a.cuda() for a in w2)
+    y = A.fused_experts(x.cuda(), w1d, w2d, torch.from_numpy(w).cuda(),
+                        torch.from_numpy(ids).cuda())
+    torch.cuda.synchronize()
+    y = y.cpu().numpy()
+    err = O.rel_err(y, ref)
+    assert err < TOL, f"rel err {err}"
+    # whole layer through the router as well
+    y2 = A.fused_moe(x.cuda(), w1d, w2d, logits.cuda(), k, True).cpu().numpy()
+    assert O.rel_err(y2, ref) < TOL
+
+
+def test_fused_experts_expert_parallel_shards_sum(A):
+    """Two expert-parallel shards (expert_map) add up to the unsharded layer."""
+    e, h, i, t, k = 8, 256, 128, 20, 2
+    w1, w2, x, logits = _moe_case(e, h, i, t, k, seed=77)
+    w, ids, _ = O.topk_softmax(logits.numpy(), k, True)
+    wt, idt = torch.from_numpy(w).cuda(), torch.from_numpy(ids).cuda()
+    full = A.fused_experts(x.cuda(), tuple(a.cuda() for a in w1), tuple(a.cuda() for a in w2),
+                           wt, idt).float()
+    acc = torch.zeros_like(full)
+    for lo in (0, 4):
+        emap = torch.full((e,), -1, dtype=torch.int32)
+        emap[lo:lo + 4] = torch.arange(4, dtype=torch.int32)
+        w1s = tuple(a[lo:lo + 4].contiguous().cuda() for a in w1)
+        w2s = tuple(a[lo:lo + 4].contiguous().cuda() for a in w2)
+        acc += A.fused_experts(x.cuda(), w1s, w2s, wt, idt, global_num_experts=e,
+                               expert_map=emap.cuda()).float()
+    assert O.rel_err(acc.cpu().numpy(), full.cpu().numpy()) < 5e-3
