@@ -1,10 +1,10 @@
 // Small-M AWQ GEMM (decode GEMV / small batches, M <= 32): weight streaming at HBM speed.
 //
-// y[M, N] = x[M, K] @ ((q - z) * s).  A CTA owns a slab of 256 output columns and a contiguous
-// range of K (see stream_core.cuh for the tile mainloop).  The CTAs that share a slab form a
-// thread-block cluster along K (cluster size S <= 8); their fp32 partial tiles are combined
-// through distributed shared memory in rank order, so split-K needs no global scratch and no
-// atomics, and the result is bit-reproducible.
+// y[M, N] = x[M, K] @ ((q - z) * s).  A CTA owns a slab of 256 output columns; the K range is
+// split over the S CTAs of a thread-block cluster (S <= 8) and, inside a CTA, over WG
+// independent warp groups (see stream_core.cuh for the tile mainloop each group runs).  The
+// S * WG fp32 partial tiles are combined through distributed shared memory in a fixed order,
+// so split-K needs no global scratch and no atomics, and the result is bit-reproducible.
 #include <cooperative_groups.h>
 
 #include "stream_core.cuh"
@@ -27,20 +27,28 @@ struct StreamParams {
   int M, N, K, group;
 };
 
-template <int MT, bool EXACT>
-__global__ void __launch_bounds__(kThreads, 2) gemm_stream_kernel(const StreamParams p) {
+constexpr int min_blocks(int MT, int WG) {
+  return WG == 1 ? (MT == 1 ? 4 : (MT == 2 ? 3 : 2)) : (MT == 1 ? 2 : 1);
+}
+
+template <int MT, bool EXACT, int GROUP, int WG>
+__global__ void __launch_bounds__(kGroupThreads * WG, min_blocks(MT, WG))
+gemm_stream_kernel(const StreamParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int kRing = Cfg<MT>::kSmemBytes;  // bytes of one warp group's ring / partial tile
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
   const int S = (int)cluster.num_blocks();
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wg = threadIdx.x / kGroupThreads;
+  const int tid = threadIdx.x % kGroupThreads, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2;
   const int words = p.N / kPack;
   const int word0 = blockIdx.y * (kBN / kPack);
   const int KT = p.K / kBK;
-  const int st_begin = (int)(((long long)rank * KT) / S);
-  const int st_end = (int)(((long long)(rank + 1) * KT) / S);
+  const int vrank = rank * WG + wg, VS = S * WG;  // this warp group's share of K
+  const int st_begin = (int)(((long long)vrank * KT) / VS);
+  const int st_end = (int)(((long long)(vrank + 1) * KT) / VS);
 
   TileSrc<MT> src;
   {
@@ -63,19 +71,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_stream_kernel(const StreamPa
   }
 
   float tot[MT][4][4];
-  mainloop<MT, EXACT>(src, smem_u32(smem), st_begin, st_end - st_begin, p.group, p.K / p.group,
-                      tot);
+  mainloop<MT, EXACT, GROUP>(src, smem_u32(smem) + wg * kRing, tid, wg, st_begin,
+                             st_end - st_begin, p.group, p.K / p.group, tot);
 
-  // ---- cluster reduction through distributed shared memory ----
+  // ---- reduction over warp groups and cluster ranks through (distributed) shared memory ----
   float* red = reinterpret_cast<float*>(smem);
-  store_tile<MT>(red, tot);
+  store_tile<MT>(red + wg * (kRing / 4), tid, tot);
   cluster.sync();
   {
     constexpr int kUnits = kBN / 8;  // 8-column units in the slab
     const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
     const int nun = uend - ubeg;
     const int n_slab = blockIdx.y * kBN;
-    for (int idx = tid; idx < nun * MT * 8; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < nun * MT * 8; idx += kGroupThreads * WG) {
       const int u = ubeg + idx % nun, m = idx / nun;
       const int n = n_slab + u * 8;
       if (m >= p.M || n >= p.N) continue;
@@ -84,10 +92,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_stream_kernel(const StreamPa
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
       for (int q = 0; q < S; ++q) {
         const float* peer = cluster.map_shared_rank(red, q) + m * kRedPitch + u * 8;
-        const float4 a = *reinterpret_cast<const float4*>(peer);
-        const float4 b = *reinterpret_cast<const float4*>(peer + 4);
-        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+#pragma unroll
+        for (int w = 0; w < WG; ++w) {
+          const float4 a = *reinterpret_cast<const float4*>(peer + w * (kRing / 4));
+          const float4 b = *reinterpret_cast<const float4*>(peer + w * (kRing / 4) + 4);
+          v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+          v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+        }
       }
       if (p.bias != nullptr) {
         const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
@@ -104,29 +115,24 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_stream_kernel(const StreamPa
   cluster.sync();  // keep this CTA's shared memory alive until every peer has read it
 }
 
-template <int MT, bool EXACT>
-int launch_variant(const StreamParams& p, cudaStream_t stream) {
-  constexpr int smem = Cfg<MT>::kSmemBytes;
+template <int MT, bool EXACT, int GROUP, int WG>
+int launch_variant(const StreamParams& p, int S, cudaStream_t stream) {
+  constexpr int smem = Cfg<MT>::kSmemBytes * WG;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  auto kernel = gemm_stream_kernel<MT, EXACT, GROUP, WG>;
   if (!attr_done[dev]) {
-    if (cudaFuncSetAttribute(gemm_stream_kernel<MT, EXACT>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
   }
   const int slabs = (p.N + kBN - 1) / kBN;
-  const int KT = p.K / kBK;
-  const int ctas_per_sm = smem <= 110 * 1024 ? 2 : 1;
-  int S = (ctas_per_sm * sm_count()) / slabs;
-  S = S < 1 ? 1 : (S > 8 ? 8 : S);
-  if (S > KT) S = KT;
-
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S, slabs, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kGroupThreads * WG, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -136,18 +142,41 @@ int launch_variant(const StreamParams& p, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm_stream_kernel<MT, EXACT>, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
     cudaGetLastError();
     return AWQ_B200_ERR_LAUNCH;
   }
   return AWQ_B200_OK;
 }
 
-template <bool EXACT>
+// Split of K: S cluster ranks x WG warp groups, sized so that about 3-4 warp groups are
+// resident per SM (that is what the shared-memory rings allow) without starving a group of
+// stages.
+template <int MT, bool EXACT, int GROUP>
+int launch_split(const StreamParams& p, cudaStream_t stream) {
+  const int slabs = (p.N + kBN - 1) / kBN;
+  const int KT = p.K / kBK;
+  const int want = (MT == 1 ? 4 : 3) * sm_count();  // warp groups in flight
+  int S = want / slabs;
+  S = S < 1 ? 1 : (S > 8 ? 8 : S);
+  if (S > KT) S = KT;
+  const bool two = MT <= 2 && slabs * S * 2 <= want && KT >= 2 * S * 2;
+  if (two) return launch_variant<MT, EXACT, GROUP, 2>(p, S, stream);
+  return launch_variant<MT, EXACT, GROUP, 1>(p, S, stream);
+}
+
+template <bool EXACT, int GROUP>
 int launch_by_m(const StreamParams& p, cudaStream_t stream) {
-  if (p.M <= 8) return launch_variant<1, EXACT>(p, stream);
-  if (p.M <= 16) return launch_variant<2, EXACT>(p, stream);
-  return launch_variant<4, EXACT>(p, stream);
+  if (p.M <= 8) return launch_split<1, EXACT, GROUP>(p, stream);
+  if (p.M <= 16) return launch_split<2, EXACT, GROUP>(p, stream);
+  return launch_variant<4, EXACT, GROUP, 1>(
+      p, [&] {
+        const int slabs = (p.N + kBN - 1) / kBN, KT = p.K / kBK;
+        int S = (2 * sm_count()) / slabs;
+        S = S < 1 ? 1 : (S > 8 ? 8 : S);
+        return S > KT ? KT : S;
+      }(),
+      stream);
 }
 
 }  // namespace
@@ -177,7 +206,9 @@ int launch_gemm_stream(const __half* x, const uint32_t* qweight, const __half* s
                        int K, int group, bool exact, cudaStream_t stream) {
   if (!gemm_stream_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
   StreamParams p{x, qweight, scales, qzeros, bias, out, M, N, K, group};
-  return exact ? launch_by_m<true>(p, stream) : launch_by_m<false>(p, stream);
+  if (group == 128)
+    return exact ? launch_by_m<true, 128>(p, stream) : launch_by_m<false, 128>(p, stream);
+  return exact ? launch_by_m<true, 0>(p, stream) : launch_by_m<false, 0>(p, stream);
 }
 
 }  // namespace awq

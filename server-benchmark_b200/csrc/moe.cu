@@ -235,10 +235,11 @@ __global__ void __launch_bounds__(kThreads, 2) moe_gemm1_kernel(const Gemm1Param
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
 
   float tot[MT][4][4];
-  mainloop<MT, kMoeExact>(src, smem_u32(smem), st_begin, st_end - st_begin, p.group, groups, tot);
+  mainloop<MT, kMoeExact, 0>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
+                              groups, tot);
 
   float* red = reinterpret_cast<float*>(smem);
-  store_tile<MT>(red, tot);
+  store_tile<MT>(red, tid, tot);
   cluster.sync();
   {
     constexpr int kUnits = 16;  // 8-column units of the 128 activation columns
@@ -332,10 +333,11 @@ __global__ void __launch_bounds__(kThreads, 2) moe_gemm2_kernel(const Gemm2Param
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
 
   float tot[MT][4][4];
-  mainloop<MT, kMoeExact>(src, smem_u32(smem), st_begin, st_end - st_begin, p.group, groups, tot);
+  mainloop<MT, kMoeExact, 0>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
+                              groups, tot);
 
   float* red = reinterpret_cast<float*>(smem);
-  store_tile<MT>(red, tot);
+  store_tile<MT>(red, tid, tot);
   cluster.sync();
   {
     constexpr int kUnits = kBN / 8;

@@ -6,10 +6,14 @@
 // mma.sync.m16n8k16, the (padded) tokens the 8-wide B operand.
 //
 //   * Stage = 128 weight rows x 128 B (32 packed words = 256 columns) + 8*MT rows of x,
-//     brought in by a 4-deep cp.async ring.
+//     brought in by a 3-deep cp.async ring.  The ring belongs to one warp group (4 warps, 128
+//     threads) that synchronises on its own named barrier, so several independent warp groups
+//     can share a CTA.
 //   * Warp w owns columns [64 w, 64 w + 64) of the slab; lane (g = lane / 4, t = lane % 4) owns
-//     packed word g of those 8 words and rows {2t, 2t+1, 2t+8, 2t+9} of every 16-row step --
-//     exactly the k slots its A fragment needs, so no data moves between lanes.
+//     packed word g of those 8 words and rows 4t .. 4t+3 of every 16-row step.  The MMA's k
+//     slots (2t, 2t+1, 2t+8, 2t+9) are mapped to those four rows -- a sum over k does not care
+//     about the order -- so no data moves between lanes and the matching x values are one
+//     8-byte shared-memory load.
 //
 // Register-only unpack (AWQ order): the low 16 bits of a word hold columns 0,2,4,6 and the
 // high 16 bits columns 1,3,5,7.  prmt pairs the low halves of two rows (k, k+1) into one
@@ -26,8 +30,8 @@
 // Both accumulate every group in fp32 and apply the fp16 scale in fp32.
 //
 // Shared-memory layout of a weight stage: row r (128 B) at r * 128, its 16-byte chunk c stored
-// at chunk position c ^ (r & 7) (the 128-byte swizzle a TMA tile load produces) --
-// conflict-free for the 4-byte reads above.  x stage: [8 MT rows][128 + 8 halves].
+// at chunk position c ^ (2 * ((r / 4) % 4) + r % 2) -- conflict-free both for the 16-byte
+// cp.async writes and for the 4-byte fragment reads.  x stage: [8 MT rows][128 + 16 halves].
 #pragma once
 
 #include "common.cuh"
@@ -39,9 +43,10 @@ constexpr int kBN = 256;      // columns per CTA slab
 constexpr int kBK = 128;      // weight rows per stage
 constexpr int kThreads = 128;
 constexpr int kWStageBytes = kBK * (kBN / kPack) * 4;  // 16384
-constexpr int kXPitch = kBK + 8;                       // halves
+constexpr int kXPitch = kBK + 16;                      // halves (row pitch = 8 words mod 32)
 constexpr int kRedPitch = kBN + 8;                     // floats
-constexpr int kStages = 4;
+constexpr int kStages = 3;
+constexpr int kGroupThreads = 128;  // one warp group
 
 template <int MT>
 struct Cfg {
@@ -55,6 +60,18 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+// barrier among the 128 threads of warp group `wg` (barrier 0 stays __syncthreads)
+__device__ __forceinline__ void group_sync(int wg) {
+  asm volatile("bar.sync %0, %1;" ::"r"(wg + 1), "n"(kGroupThreads) : "memory");
+}
+__device__ __forceinline__ uint32_t row_swizzle(int row) {
+  return (uint32_t)((((row >> 2) & 3) << 1) | (row & 1));
 }
 
 // What one thread needs to know about the operands of its CTA tile.
@@ -77,13 +94,16 @@ struct TileSrc {
 // Runs stages [st_begin, st_begin + nst) and leaves the fp32 tile in `tot`:
 //   tot[mt][i][0], [1] = column 2i   of this lane's word, tokens 8 mt + 2t, 8 mt + 2t + 1
 //   tot[mt][i][2], [3] = column 2i+1 of this lane's word, same tokens
-template <int MT, bool EXACT>
-__device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_base, int st_begin,
-                                         int nst, int group, int ngroups,
+// GROUP is the quantisation group size when known at compile time (128: loops fully
+// unrolled) or 0 to take it from `group` at run time (32 / 64 / 128).
+// `tid` is the thread's index inside its warp group `wg`.
+template <int MT, bool EXACT, int GROUP>
+__device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_base, int tid,
+                                         int wg, int st_begin, int nst, int group, int ngroups,
                                          float (&tot)[MT][4][4]) {
   constexpr int STAGES = kStages;
   constexpr int STAGE = Cfg<MT>::kStageBytes;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
   auto issue_stage = [&](int st, int buf) {
@@ -94,7 +114,7 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int row = rbase + 16 * i;
-      cp_async16(wbase + row * 128 + ((chunk ^ (row & 7)) << 4), s0 + (size_t)row * src.wrow_words,
+      cp_async16(wbase + row * 128 + ((chunk ^ row_swizzle(row)) << 4), s0 + (size_t)row * src.wrow_words,
                  src.wvalid);
     }
     const uint32_t xbase = wbase + kWStageBytes;
@@ -106,10 +126,10 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
   };
 
   const int chunk_id = 2 * warp + (g >> 2);
-  const uint32_t offA = ((chunk_id ^ (2 * t)) << 4) + (g & 3) * 4;
-  const uint32_t offB = ((chunk_id ^ (2 * t + 1)) << 4) + (g & 3) * 4;
-  const int spg = group / 16;   // 16-row steps per quantisation group
-  const int gps = kBK / group;  // groups per stage
+  const uint32_t offA = ((chunk_id ^ (2 * t)) << 4) + (g & 3) * 4;      // even rows
+  const uint32_t offB = ((chunk_id ^ (2 * t + 1)) << 4) + (g & 3) * 4;  // odd rows
+  const int spg = GROUP ? GROUP / 16 : group / 16;   // 16-row steps per quantisation group
+  const int gps = GROUP ? kBK / GROUP : kBK / group;  // groups per stage
 
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -135,7 +155,7 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
 
   for (int it = 0; it < nst; ++it) {
     cp_async_wait<STAGES - 2>();
-    __syncthreads();
+    group_sync(wg);
     {
       const int nx = it + STAGES - 1;
       if (nx < nst) issue_stage(st_begin + nx, nx % STAGES);
@@ -182,19 +202,21 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
         zv[3] = __hmul2(as_half2(lop3_and_or(vz >> 8, 0x00F000F0u, 0x64006400u)), m16);
       }
 
-      for (int s2 = 0; s2 < spg; ++s2) {
+#pragma unroll
+      for (int s2 = 0; s2 < (GROUP ? GROUP / 16 : 8); ++s2) {
+        if (!GROUP && s2 >= spg) break;
         const int s = gi * spg + s2;
-        const uint32_t rowA = wsm + (16 * s + 2 * t) * 128;
+        const uint32_t rowA = wsm + (16 * s + 4 * t) * 128;
         const uint32_t w0 = lds32(rowA + offA);
         const uint32_t w1 = lds32(rowA + 128 + offB);
-        const uint32_t w2 = lds32(rowA + 8 * 128 + offA);
-        const uint32_t w3 = lds32(rowA + 9 * 128 + offB);
+        const uint32_t w2 = lds32(rowA + 2 * 128 + offA);
+        const uint32_t w3 = lds32(rowA + 3 * 128 + offB);
         uint32_t b0[MT], b1[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          const uint32_t xa = xsm + ((mt * 8 + g) * kXPitch + 16 * s + 2 * t) * 2;
-          b0[mt] = lds32(xa);
-          b1[mt] = lds32(xa + 16);
+          const uint2 xv = lds64(xsm + ((mt * 8 + g) * kXPitch + 16 * s + 4 * t) * 2);
+          b0[mt] = xv.x;
+          b1[mt] = xv.y;
         }
         const uint32_t u0 = prmt(w0, w1, 0x5410), v0 = prmt(w0, w1, 0x7632);
         const uint32_t u1 = prmt(w2, w3, 0x5410), v1 = prmt(w2, w3, 0x7632);
@@ -270,13 +292,13 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
     }
   }
   cp_async_wait<0>();
-  __syncthreads();  // every warp is done with the ring: it may be reused by the caller
+  group_sync(wg);  // every warp of the group is done with the ring: the caller may reuse it
 }
 
 // Writes the register tile to shared memory as red[m][col] (pitch kRedPitch floats).
 template <int MT>
-__device__ __forceinline__ void store_tile(float* red, const float (&tot)[MT][4][4]) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ void store_tile(float* red, int tid, const float (&tot)[MT][4][4]) {
+  const int lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)

@@ -94,9 +94,12 @@ def test_moe_align_against_installed_vllm(A):
     assert post.item() == vpost.item()
     nb = post.item() // blk
     assert torch.equal(eid[:nb], veid[:nb])
-    a = s[:post.item()].reshape(nb, blk).sort(dim=1).values
-    b = vs[:post.item()].reshape(nb, blk).sort(dim=1).values
-    assert torch.equal(a, b)   # same per-block sets; within-block order is ours (ascending)
+    # same set of pairs per expert; the order inside an expert's run is ours (ascending)
+    a = s[:post.item()].cpu().numpy().reshape(nb, blk)
+    b = vs[:post.item()].cpu().numpy().reshape(nb, blk)
+    ee = eid[:nb].cpu().numpy()
+    for x in np.unique(ee):
+        assert sorted(a[ee == x].reshape(-1).tolist()) == sorted(b[ee == x].reshape(-1).tolist())
 
 
 def _moe_case(e, h, i, t, k, seed):
