@@ -82,6 +82,14 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Health word of the tcgen05 kernel on the current device.  Its mbarrier waits are bounded;
+ * a wait that ran out records which one (1 producer, 2-3 MMA issuer, 4 dequantisation,
+ * 5 epilogue) and the kernel tears down instead of hanging.  0 = no wait ever ran out.
+ * Synchronises the device (a plain device-to-host copy).  No counterpart in the reference.
+ */
+int awq_b200_device_status(int* status);
+
+/*
  * Router: softmax over E experts, top-k (ties: lower expert id first), optional
  * renormalisation of the k weights.  gating is fp32 (gating_dtype 0) or fp16 (1), [T, E].
  * Outputs: topk_weights fp32 [T, k], topk_ids int32 [T, k], token_expert_indices int32 [T, k]

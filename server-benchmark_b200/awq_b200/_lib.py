@@ -28,6 +28,7 @@ PROTOTYPES = {
     "awq_b200_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "awq_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "awq_b200_device_status": (c_int, [POINTER(c_int)]),
     "awq_b200_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_void_p]),
     "awq_b200_moe_sorted_capacity": (c_int64, [c_int64, c_int, c_int]),

@@ -122,6 +122,12 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
   }
 }
 
+int awq_b200_device_status(int* status) {
+  if (!status) return AWQ_B200_ERR_NULL;
+  if (int rc = check_device()) return rc;
+  return awq::tc_device_status(status);
+}
+
 int awq_b200_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                           int renormalize, float* topk_weights, int32_t* topk_ids,
                           int32_t* token_expert_indices, void* stream) {

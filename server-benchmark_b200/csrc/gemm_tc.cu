@@ -1,10 +1,428 @@
-// placeholder until the tcgen05 kernel lands
+// Large-M AWQ GEMM on the 5th-generation tensor cores (tcgen05 / TMEM), weights dequantised in
+// shared memory.
+//
+//   y[M, N] = x[M, K] @ ((q - z) * s)
+//
+// CTA tile: 128 tokens x BN columns (BN = 256 or 128), K walked in stages of 64.
+//   D (TMEM, fp32, 128 lanes x BN columns) += A (smem) * B (smem)      tcgen05.mma kind::f16
+//     A = x tile [128 x 64] fp16, K-major, 128-byte swizzle, written by TMA.
+//     B = W tile [64 x BN] fp16, MN-major (columns contiguous, as the AWQ packing delivers
+//         them), 128-byte swizzle: per block of 64 columns a [64 rows x 128 B] region, 16-byte
+//         chunk c of row k stored at c ^ (k & 7).  Written by the dequantisation warps.
+//   The packed weights [64 x BN/8 words] arrive by TMA (no swizzle) next to A.
+//
+// Warp roles (192 threads):
+//   warps 0-3  dequantise: one packed word -> 8 fp16 -> one 16-byte store; afterwards the
+//              epilogue: tcgen05.ld of their 32 TMEM lanes, fp16 conversion, global stores.
+//   warp 4     TMA producer (one elected lane).
+//   warp 5     TMEM allocation; one elected lane issues tcgen05.mma and tcgen05.commit.
+// mbarrier rings: full_raw[s] (TMA landed) -> full_b[s] (B tile written) -> empty[s]
+// (tcgen05.commit: the MMAs that read stage s have finished), and tmem_full for the epilogue.
+//
+// Every wait is bounded: after kSpinLimit polls a thread records a status code in
+// g_tc_status, raises the CTA's abort flag, and all roles fall through to the teardown, where
+// TMEM is freed.  Nothing here uses cluster multicast.
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace awq {
-bool gemm_tc_supported(int, int, int, int) { return false; }
-size_t gemm_tc_workspace_bytes(int, int, int, int) { return 0; }
-int launch_gemm_tc(const __half*, const uint32_t*, const __half*, const uint32_t*, const __half*,
-                   __half*, int, int, int, int, void*, size_t, cudaStream_t) {
-  return AWQ_B200_ERR_SHAPE;
+
+__device__ int g_tc_status = 0;
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBKtc = 64;
+constexpr int kTcThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 20;
+
+template <int BN>
+struct TcCfg {
+  static constexpr int kABytes = kBM * kBKtc * 2;            // 16384
+  static constexpr int kBBytes = kBKtc * BN * 2;             // 32768 / 16384
+  static constexpr int kRawBytes = kBKtc * (BN / kPack) * 4; // 8192 / 4096
+  static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
+  static constexpr int kStages = BN == 256 ? 3 : 5;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + align slack
+};
+
+struct TcParams {
+  const __half* scales;
+  const uint32_t* qzeros;
+  const __half* bias;
+  __half* out;
+  int M, N, K, group;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA has been aborted (by this thread or another).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_tc_status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte
+// offsets (all >> 4), version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const TcParams p) {
+  using C = TcCfg<BN>;
+  constexpr int STAGES = C::kStages;
+  constexpr int WPR = BN / kPack;           // packed words per weight row of the tile
+  constexpr int KSTEP = 128 / WPR;          // rows covered by the 128 dequant threads per pass
+  constexpr int PASSES = kBKtc / KSTEP;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ volatile int s_abort;
+  __shared__ uint32_t s_tmem_base;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * C::kStageBytes;
+  auto a_addr = [&](int s) { return smem_base + s * C::kStageBytes; };
+  auto b_addr = [&](int s) { return smem_base + s * C::kStageBytes + C::kABytes; };
+  auto raw_addr = [&](int s) { return smem_base + s * C::kStageBytes + C::kABytes + C::kBBytes; };
+  auto full_raw = [&](int s) { return bar_base + 8 * s; };
+  auto full_b = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  auto empty = [&](int s) { return bar_base + 8 * (2 * STAGES + s); };
+  const uint32_t tmem_full = bar_base + 8 * (3 * STAGES);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * kBM;
+  const int n0 = blockIdx.y * BN;
+  const int KT = p.K / kBKtc;
+  const int words = p.N / kPack;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_raw(s), 1);
+      mbar_init(full_b(s), 128);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(tmem_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = s_tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int kt = 0; kt < KT; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t round = (uint32_t)(kt / STAGES);
+        if (!mbar_wait(empty(s), (round & 1u) ^ 1u, &s_abort, 1)) break;
+        mbar_arrive_expect_tx(full_raw(s), C::kABytes + C::kRawBytes);
+        tma_load_2d(a_addr(s), &map_x, kt * kBKtc, m0, full_raw(s));
+        tma_load_2d(raw_addr(s), &map_w, n0 / kPack, kt * kBKtc, full_raw(s));
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D fp32, A/B fp16, A K-major, B MN-major, N = BN, M = 128
+      constexpr uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                 ((uint32_t)(kBM >> 4) << 24);
+      bool ok = true;
+      for (int kt = 0; kt < KT && ok; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t round = (uint32_t)(kt / STAGES);
+        ok = mbar_wait(full_raw(s), round & 1u, &s_abort, 2) &&
+             mbar_wait(full_b(s), round & 1u, &s_abort, 3);
+        if (!ok) break;
+        tc_fence_after();
+        // A: K-major SW128, 8-row core blocks 1024 B apart; B: MN-major SW128, 64-column
+        // blocks 8192 B apart (LBO), 8-row k blocks 1024 B apart (SBO).
+        const uint64_t da = make_desc(a_addr(s), 16, 1024);
+        const uint64_t db = make_desc(b_addr(s), 8192, 1024);
+#pragma unroll
+        for (int k16 = 0; k16 < kBKtc / 16; ++k16) {
+          // advance 16 k: +32 B inside A's 128-byte rows, +16 rows (2048 B) in B
+          umma_f16_ss(tmem_d, da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 2048) >> 4),
+                      idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+        }
+        umma_commit(empty(s));
+      }
+      if (ok) umma_commit(tmem_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ dequant warps 0-3
+    const int c = tid % WPR;            // packed word column inside the tile
+    const int krow0 = tid / WPR;
+    const int wcol = min(n0 / kPack + c, words - 1);  // clamped past the N edge
+    const uint32_t b_off = (uint32_t)(c / 8) * (kBKtc * 128) ;  // 64-column block
+    const uint32_t chunk = (uint32_t)(c & 7);
+    int cur_group = -1;
+    __half2 zE0, zO0, zE1, zO1, sE0, sO0, sE1, sO1;
+    bool ok = true;
+    for (int kt = 0; kt < KT && ok; ++kt) {
+      const int s = kt % STAGES;
+      const uint32_t round = (uint32_t)(kt / STAGES);
+      const int grp = (kt * kBKtc) / p.group;
+      if (grp != cur_group) {
+        cur_group = grp;
+        const uint32_t zw = __ldg(p.qzeros + (size_t)grp * words + wcol);
+        const uint4 sv = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)grp * p.N) + wcol);
+        const uint32_t zw8 = zw >> 8;
+        zE0 = as_half2(lop3_and_or(zw, 0x000F000Fu, 0x64006400u));   // 1024 + z, cols 0,1
+        zO0 = as_half2(lop3_and_or(zw, 0x00F000F0u, 0x64006400u));   // 1024 + 16 z, cols 2,3
+        zE1 = as_half2(lop3_and_or(zw8, 0x000F000Fu, 0x64006400u));  // cols 4,5
+        zO1 = as_half2(lop3_and_or(zw8, 0x00F000F0u, 0x64006400u));  // cols 6,7
+        const __half2 r16 = __float2half2_rn(0.0625f);
+        sE0 = as_half2(sv.x);
+        sO0 = __hmul2(as_half2(sv.y), r16);  // nibbles kept in place carry a factor 16
+        sE1 = as_half2(sv.z);
+        sO1 = __hmul2(as_half2(sv.w), r16);
+      }
+      ok = mbar_wait(full_raw(s), round & 1u, &s_abort, 4);
+      if (!ok) break;
+      const uint32_t raw = raw_addr(s), bt = b_addr(s) + b_off;
+#pragma unroll
+      for (int j = 0; j < PASSES; ++j) {
+        const int k = krow0 + KSTEP * j;
+        uint32_t w;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"(raw + (k * WPR + c) * 4));
+        const uint32_t w8 = w >> 8;
+        uint4 o;
+        o.x = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w, 0x000F000Fu, 0x64006400u)), zE0), sE0));
+        o.y = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w, 0x00F000F0u, 0x64006400u)), zO0), sO0));
+        o.z = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w8, 0x000F000Fu, 0x64006400u)), zE1), sE1));
+        o.w = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w8, 0x00F000F0u, 0x64006400u)), zO1), sO1));
+        const uint32_t dst = bt + k * 128 + ((chunk ^ (uint32_t)(k & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o.x), "r"(o.y),
+                     "r"(o.z), "r"(o.w)
+                     : "memory");
+      }
+      fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
+      mbar_arrive(full_b(s));
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    if (ok && mbar_wait(tmem_full, 0, &s_abort, 5)) {
+      tc_fence_after();
+      const int m = m0 + warp * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+            "[%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+              "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+              "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int n = n0 + c0;
+        if (m < p.M && n < p.N) {
+          __align__(16) __half2 h[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+            if (p.bias != nullptr) {
+              const __half2 b = __ldg(reinterpret_cast<const __half2*>(p.bias + n) + j);
+              v0 += __low2float(b);
+              v1 += __high2float(b);
+            }
+            h[j] = __floats2half2_rn(v0, v1);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n);
+          const uint4* srcv = reinterpret_cast<const uint4*>(h);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = srcv[j];
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d),
+                 "r"((uint32_t)BN)
+                 : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+template <int BN>
+int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, cudaStream_t stream) {
+  using C = TcCfg<BN>;
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return AWQ_B200_ERR_DRIVER;
+  CUtensorMap map_x, map_w;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBKtc, (cuuint32_t)kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return AWQ_B200_ERR_DRIVER;
+  }
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)(p.N / kPack), (cuuint64_t)p.K};
+    const cuuint64_t strides[1] = {(cuuint64_t)(p.N / kPack) * 4};
+    const cuuint32_t box[2] = {(cuuint32_t)(BN / kPack), (cuuint32_t)kBKtc};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<uint32_t*>(qweight), dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return AWQ_B200_ERR_DRIVER;
+  }
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  if (!attr_done[dev]) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::kSmemBytes) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+    attr_done[dev] = true;
+  }
+  dim3 grid((p.M + kBM - 1) / kBM, (p.N + BN - 1) / BN, 1);
+  gemm_tc_kernel<BN><<<grid, kTcThreads, C::kSmemBytes, stream>>>(map_x, map_w, p);
+  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(int M, int N, int K, int group) {
+  // TMA needs 16-byte row pitches (K % 8, N % 32); a stage is 64 rows of K and must not
+  // straddle quantisation groups.
+  return M >= 1 && N % 32 == 0 && K % kBKtc == 0 && (group == 128 || group == 64) &&
+         (M + kBM - 1) / kBM <= 65535;
+}
+
+size_t gemm_tc_workspace_bytes(int, int, int, int) { return 0; }
+
+int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scales,
+                   const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
+                   int group, void*, size_t, cudaStream_t stream) {
+  if (!gemm_tc_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+  TcParams p{scales, qzeros, bias, out, M, N, K, group};
+  // 128-column tiles when 256-column tiles would leave most SMs idle
+  const long tiles256 = (long)((M + kBM - 1) / kBM) * ((N + 255) / 256);
+  if (tiles256 < sm_count()) return launch_tc<128>(x, qweight, p, stream);
+  return launch_tc<256>(x, qweight, p, stream);
+}
+
+int tc_device_status(int* out) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
+  *out = v;
+  return AWQ_B200_OK;
+}
+
 }  // namespace awq
