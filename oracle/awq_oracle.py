@@ -99,6 +99,27 @@ def awq_gemm_fp32(x, qweight, scales, qzeros, group: int = 128) -> np.ndarray:
     return (xt @ w).numpy()
 
 
+def awq_gemm_fp32_torch(x, qweight, scales, qzeros, group: int = 128):
+    """The same dequantise-then-matmul written with torch tensor ops only (torch CPU tensors in,
+    fp32 torch tensor out), so that every step runs on all host threads.  This is the form timed
+    as the CPU baseline; tests check it against the numpy functions above.
+
+    vLLM: awq_triton.py:54-101 (unpack order, (q - z) * s), awq.py:276-283 (call site).
+    """
+    import torch
+
+    shifts = torch.tensor([4 * int(r) for r in AWQ_REVERSE], dtype=torch.int32)
+
+    def unpack(t):
+        r, c = t.shape
+        return ((t.unsqueeze(-1) >> shifts) & 0xF).reshape(r, c * PACK)
+
+    q = unpack(qweight)
+    z = unpack(qzeros).repeat_interleave(group, dim=0)
+    w = (q - z).to(torch.float32) * scales.to(torch.float32).repeat_interleave(group, dim=0)
+    return x.to(torch.float32) @ w
+
+
 def awq_linear(x, qweight, scales, qzeros, bias=None, group: int = 128) -> np.ndarray:
     """AWQLinearMethod.apply: fp16 output, optional bias added after the product.
 

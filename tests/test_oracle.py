@@ -119,3 +119,13 @@ def test_fused_experts_against_dense_loop():
             act = a[:i] / (1 + np.exp(-a[:i])) * a[i:]
             ref[tt] += w[tt, s] * (act @ O.dequantize_fp32(w2_q[ee], w2_s[ee], w2_z[ee]))
     assert O.rel_err(y, ref) < 1e-4
+
+
+def test_torch_form_of_the_oracle_matches_numpy_form(golden):
+    import torch
+    for name in CASES:
+        g = int(golden[f"{name}.group"][0])
+        a = [golden[f"{name}.{k}"] for k in ("x", "qweight", "scales", "qzeros")]
+        y_np = O.awq_gemm_fp32(*a, g)
+        y_t = O.awq_gemm_fp32_torch(*[torch.from_numpy(v) for v in a], g).numpy()
+        assert np.allclose(y_np, y_t, rtol=1e-5, atol=1e-5)
