@@ -3,28 +3,37 @@
 //
 //   y[M, N] = x[M, K] @ ((q - z) * s)
 //
-// CTA tile: 128 tokens x BN columns (BN = 256 or 128), K walked in stages of 64.
-//   D (TMEM, fp32, 128 lanes x BN columns) += A (smem) * B (smem)      tcgen05.mma kind::f16
-//     A = x tile [128 x 64] fp16, K-major, 128-byte swizzle, written by TMA.
-//     B = W tile [64 x BN] fp16, MN-major (columns contiguous, as the AWQ packing delivers
-//         them), 128-byte swizzle: per block of 64 columns a [64 rows x 128 B] region, 16-byte
-//         chunk c of row k stored at c ^ (k & 7).  Written by the dequantisation warps.
+// CTA tile: (128 * MT) tokens x BN columns (MT = 1 or 2, BN = 256 or 128), K walked in stages of
+// 64 rows.  Per stage
+//   D_mt (TMEM, fp32, 128 lanes x BN columns) += A_mt (smem) * B (smem)    tcgen05.mma kind::f16
+//     A_mt = x tile [128 x 64] fp16, K-major, 128-byte swizzle, written by TMA.
+//     B    = W tile [64 x BN] fp16, MN-major (columns contiguous, as the AWQ packing delivers
+//            them), 128-byte swizzle: per block of 64 columns a [64 rows x 128 B] region, 16-byte
+//            chunk c of row k stored at c ^ (k & 7).  Written by the dequantisation warps; with
+//            MT = 2 one dequantised tile feeds two MMAs, halving the conversion work per flop.
 //   The packed weights [64 x BN/8 words] arrive by TMA (no swizzle) next to A.
 //
-// Warp roles (192 threads):
-//   warps 0-3  dequantise: one packed word -> 8 fp16 -> one 16-byte store; afterwards the
-//              epilogue: tcgen05.ld of their 32 TMEM lanes, fp16 conversion, global stores.
-//   warp 4     TMA producer (one elected lane).
-//   warp 5     TMEM allocation; one elected lane issues tcgen05.mma and tcgen05.commit.
+// Warp roles (320 threads):
+//   warps 0-7  dequantise: one packed word -> 8 fp16 -> one 16-byte store; afterwards the
+//              epilogue: tcgen05.ld of their TMEM lane quarter, fp16 conversion, global stores.
+//   warp 8     TMA producer (one elected lane).
+//   warp 9     TMEM allocation; one elected lane issues tcgen05.mma and tcgen05.commit.
 // mbarrier rings: full_raw[s] (TMA landed) -> full_b[s] (B tile written) -> empty[s]
 // (tcgen05.commit: the MMAs that read stage s have finished), and tmem_full for the epilogue.
+//
+// Split-K (MT = 1 only): the Z CTAs of a thread-block cluster take consecutive K ranges of the
+// same tile; their fp32 accumulators are spilled to shared memory and summed through
+// distributed shared memory in rank order (deterministic, no global scratch).
 //
 // Every wait is bounded: after kSpinLimit polls a thread records a status code in
 // g_tc_status, raises the CTA's abort flag, and all roles fall through to the teardown, where
 // TMEM is freed.  Nothing here uses cluster multicast.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace awq {
 
@@ -34,18 +43,25 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBKtc = 64;
-constexpr int kTcThreads = 192;
+constexpr int kDqWarps = 8;
+constexpr int kDqThreads = kDqWarps * 32;
+constexpr int kTcThreads = kDqThreads + 64;
 constexpr uint32_t kSpinLimit = 1u << 20;
 
-template <int BN>
+template <int BN, int MT>
 struct TcCfg {
-  static constexpr int kABytes = kBM * kBKtc * 2;            // 16384
-  static constexpr int kBBytes = kBKtc * BN * 2;             // 32768 / 16384
-  static constexpr int kRawBytes = kBKtc * (BN / kPack) * 4; // 8192 / 4096
+  static constexpr int kABytes = MT * kBM * kBKtc * 2;        // 16384 per 128-row tile
+  static constexpr int kBBytes = kBKtc * BN * 2;              // 32768 / 16384
+  static constexpr int kRawBytes = kBKtc * (BN / kPack) * 4;  // 8192 / 4096
   static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
-  static constexpr int kStages = BN == 256 ? 3 : 5;
+  static constexpr int kStages = (BN == 256) ? 3 : (MT == 2 ? 4 : 5);
   static constexpr int kBarBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + align slack
+  static constexpr int kRedPitch = BN + 4;  // floats, split-K spill tile
+  static constexpr int kRedBytes = kBM * kRedPitch * 4;
+  static constexpr int kPipeBytes = kStages * kStageBytes;
+  static constexpr int kMainBytes = kPipeBytes > kRedBytes ? kPipeBytes : kRedBytes;
+  static constexpr int kSmemBytes = kMainBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kTmemCols = BN * MT;
 };
 
 struct TcParams {
@@ -120,6 +136,21 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+      "[%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte
 // offsets (all >> 4), version 1, 128-byte swizzle.
@@ -134,21 +165,25 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const TcParams p) {
-  using C = TcCfg<BN>;
+  using C = TcCfg<BN, MT>;
   constexpr int STAGES = C::kStages;
-  constexpr int WPR = BN / kPack;           // packed words per weight row of the tile
-  constexpr int KSTEP = 128 / WPR;          // rows covered by the 128 dequant threads per pass
+  constexpr int WPR = BN / kPack;             // packed words per weight row of the tile
+  constexpr int KSTEP = kDqThreads / WPR;     // rows covered by the dequant threads per pass
   constexpr int PASSES = kBKtc / KSTEP;
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int s_abort;
   __shared__ uint32_t s_tmem_base;
 
+  cg::cluster_group cluster = cg::this_cluster();
+  const int zrank = (int)cluster.block_rank();
+  const int Z = (int)cluster.num_blocks();
+
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + STAGES * C::kStageBytes;
+  const uint32_t bar_base = smem_base + C::kMainBytes;
   auto a_addr = [&](int s) { return smem_base + s * C::kStageBytes; };
   auto b_addr = [&](int s) { return smem_base + s * C::kStageBytes + C::kABytes; };
   auto raw_addr = [&](int s) { return smem_base + s * C::kStageBytes + C::kABytes + C::kBBytes; };
@@ -158,26 +193,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tmem_full = bar_base + 8 * (3 * STAGES);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * kBM;
+  const int m0 = blockIdx.x * (kBM * MT);
   const int n0 = blockIdx.y * BN;
-  const int KT = p.K / kBKtc;
+  const int KT_all = p.K / kBKtc;
+  const int kt_begin = (int)(((long long)zrank * KT_all) / Z);
+  const int kt_end = (int)(((long long)(zrank + 1) * KT_all) / Z);
+  const int KT = kt_end - kt_begin;
   const int words = p.N / kPack;
 
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_raw(s), 1);
-      mbar_init(full_b(s), 128);
+      mbar_init(full_b(s), kDqThreads);
       mbar_init(empty(s), 1);
     }
     mbar_init(tmem_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  if (warp == 5) {
+  if (warp == kDqWarps + 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)C::kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -185,61 +223,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = s_tmem_base;
+  bool ok = true;
 
-  if (warp == 4) {
+  if (warp == kDqWarps) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int kt = 0; kt < KT; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t round = (uint32_t)(kt / STAGES);
+      for (int it = 0; it < KT; ++it) {
+        const int s = it % STAGES;
+        const uint32_t round = (uint32_t)(it / STAGES);
         if (!mbar_wait(empty(s), (round & 1u) ^ 1u, &s_abort, 1)) break;
+        const int k0 = (kt_begin + it) * kBKtc;
         mbar_arrive_expect_tx(full_raw(s), C::kABytes + C::kRawBytes);
-        tma_load_2d(a_addr(s), &map_x, kt * kBKtc, m0, full_raw(s));
-        tma_load_2d(raw_addr(s), &map_w, n0 / kPack, kt * kBKtc, full_raw(s));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(a_addr(s) + mt * (kBM * kBKtc * 2), &map_x, k0, m0 + mt * kBM, full_raw(s));
+        tma_load_2d(raw_addr(s), &map_w, n0 / kPack, k0, full_raw(s));
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kDqWarps + 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // instruction descriptor: D fp32, A/B fp16, A K-major, B MN-major, N = BN, M = 128
       constexpr uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
                                  ((uint32_t)(kBM >> 4) << 24);
-      bool ok = true;
-      for (int kt = 0; kt < KT && ok; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t round = (uint32_t)(kt / STAGES);
+      for (int it = 0; it < KT && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t round = (uint32_t)(it / STAGES);
         ok = mbar_wait(full_raw(s), round & 1u, &s_abort, 2) &&
              mbar_wait(full_b(s), round & 1u, &s_abort, 3);
         if (!ok) break;
         tc_fence_after();
         // A: K-major SW128, 8-row core blocks 1024 B apart; B: MN-major SW128, 64-column
         // blocks 8192 B apart (LBO), 8-row k blocks 1024 B apart (SBO).
-        const uint64_t da = make_desc(a_addr(s), 16, 1024);
         const uint64_t db = make_desc(b_addr(s), 8192, 1024);
 #pragma unroll
-        for (int k16 = 0; k16 < kBKtc / 16; ++k16) {
-          // advance 16 k: +32 B inside A's 128-byte rows, +16 rows (2048 B) in B
-          umma_f16_ss(tmem_d, da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 2048) >> 4),
-                      idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint64_t da = make_desc(a_addr(s) + mt * (kBM * kBKtc * 2), 16, 1024);
+#pragma unroll
+          for (int k16 = 0; k16 < kBKtc / 16; ++k16) {
+            // advance 16 k: +32 B inside A's 128-byte rows, +16 rows (2048 B) in B
+            umma_f16_ss(tmem_d + mt * BN, da + (uint64_t)((k16 * 32) >> 4),
+                        db + (uint64_t)((k16 * 2048) >> 4), idesc, (it > 0 || k16 > 0) ? 1u : 0u);
+          }
         }
         umma_commit(empty(s));
       }
       if (ok) umma_commit(tmem_full);
     }
   } else {
-    // ------------------------------------------------------------------ dequant warps 0-3
+    // ------------------------------------------------------------------ dequant warps
     const int c = tid % WPR;            // packed word column inside the tile
     const int krow0 = tid / WPR;
     const int wcol = min(n0 / kPack + c, words - 1);  // clamped past the N edge
-    const uint32_t b_off = (uint32_t)(c / 8) * (kBKtc * 128) ;  // 64-column block
-    const uint32_t chunk = (uint32_t)(c & 7);
+    // KSTEP is a multiple of 8, so (k & 7) is the same for every row this thread converts
+    const uint32_t b_off = (uint32_t)(c / 8) * (kBKtc * 128) + krow0 * 128 +
+                           (((uint32_t)(c & 7) ^ (uint32_t)(krow0 & 7)) << 4);
+    const uint32_t raw_off = (uint32_t)(krow0 * WPR + c) * 4;
     int cur_group = -1;
     __half2 zE0, zO0, zE1, zO1, sE0, sO0, sE1, sO1;
-    bool ok = true;
-    for (int kt = 0; kt < KT && ok; ++kt) {
-      const int s = kt % STAGES;
-      const uint32_t round = (uint32_t)(kt / STAGES);
-      const int grp = (kt * kBKtc) / p.group;
+    for (int it = 0; it < KT && ok; ++it) {
+      const int s = it % STAGES;
+      const uint32_t round = (uint32_t)(it / STAGES);
+      const int grp = ((kt_begin + it) * kBKtc) / p.group;
       if (grp != cur_group) {
         cur_group = grp;
         const uint32_t zw = __ldg(p.qzeros + (size_t)grp * words + wcol);
@@ -257,21 +302,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       ok = mbar_wait(full_raw(s), round & 1u, &s_abort, 4);
       if (!ok) break;
-      const uint32_t raw = raw_addr(s), bt = b_addr(s) + b_off;
+      const uint32_t raw = raw_addr(s) + raw_off, bt = b_addr(s) + b_off;
+      uint32_t w[PASSES];
+#pragma unroll
+      for (int j = 0; j < PASSES; ++j)
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[j]) : "r"(raw + j * (KSTEP * WPR * 4)));
 #pragma unroll
       for (int j = 0; j < PASSES; ++j) {
-        const int k = krow0 + KSTEP * j;
-        uint32_t w;
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"(raw + (k * WPR + c) * 4));
-        const uint32_t w8 = w >> 8;
+        const uint32_t w8 = w[j] >> 8;
         uint4 o;
-        o.x = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w, 0x000F000Fu, 0x64006400u)), zE0), sE0));
-        o.y = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w, 0x00F000F0u, 0x64006400u)), zO0), sO0));
+        o.x = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w[j], 0x000F000Fu, 0x64006400u)), zE0), sE0));
+        o.y = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w[j], 0x00F000F0u, 0x64006400u)), zO0), sO0));
         o.z = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w8, 0x000F000Fu, 0x64006400u)), zE1), sE1));
         o.w = as_u32(__hmul2(__hsub2(as_half2(lop3_and_or(w8, 0x00F000F0u, 0x64006400u)), zO1), sO1));
-        const uint32_t dst = bt + k * 128 + ((chunk ^ (uint32_t)(k & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o.x), "r"(o.y),
-                     "r"(o.z), "r"(o.w)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(bt + j * (KSTEP * 128)),
+                     "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
                      : "memory");
       }
       fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
@@ -279,27 +324,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
 
     // ---------------------------------------------------------------- epilogue
-    if (ok && mbar_wait(tmem_full, 0, &s_abort, 5)) {
+    // warp w reads TMEM lanes 32 (w % 4) ..; with MT = 2 warps 4-7 own the second accumulator,
+    // with MT = 1 they own the upper half of the columns.
+    const int q = warp & 3, hi = warp >> 2;
+    const int acc = MT == 2 ? hi : 0;
+    const int col_begin = MT == 2 ? 0 : hi * (BN / 2);
+    const int col_end = MT == 2 ? BN : (hi + 1) * (BN / 2);
+    const uint32_t tlane = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+    if (KT > 0) ok = ok && mbar_wait(tmem_full, 0, &s_abort, 5);
+    if (ok && Z == 1) {
       tc_fence_after();
-      const int m = m0 + warp * 32 + lane;
+      const int m = m0 + acc * kBM + q * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
-            "[%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-              "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-              "=r"(r[31])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tmem_ld32(tlane + (uint32_t)c0, r);
         const int n = n0 + c0;
         if (m < p.M && n < p.N) {
           __align__(16) __half2 h[16];
@@ -319,16 +358,72 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           for (int j = 0; j < 4; ++j) dst[j] = srcv[j];
         }
       }
+    } else if (ok && MT == 1) {
+      // split-K: spill this CTA's fp32 partial tile to shared memory (the ring is idle now)
+      tc_fence_after();
+      float* red = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+      const int row = q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+        uint32_t r[32];
+        if (KT > 0) {
+          tmem_ld32(tlane + (uint32_t)c0, r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        float4* dst = reinterpret_cast<float4*>(red + row * C::kRedPitch + c0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+      }
     }
+  }
+
+  if (MT == 1 && Z > 1) {
+    // ---------------------------------------------------------------- cluster split-K reduce
+    cluster.sync();
+    if (!s_abort) {
+      float* red = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+      constexpr int kUnits = BN / 8;
+      const int rbeg = (zrank * kBM) / Z, rend = ((zrank + 1) * kBM) / Z;
+      for (int idx = tid; idx < (rend - rbeg) * kUnits; idx += kTcThreads) {
+        const int row = rbeg + idx / kUnits, u = idx % kUnits;
+        const int m = m0 + row, n = n0 + u * 8;
+        if (m >= p.M || n >= p.N) continue;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        for (int zq = 0; zq < Z; ++zq) {
+          const float* peer = cluster.map_shared_rank(red, zq) + row * C::kRedPitch + u * 8;
+          const float4 a = *reinterpret_cast<const float4*>(peer);
+          const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+          v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+          v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+        }
+        if (p.bias != nullptr) {
+          const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+          const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += __half2float(bh[j]);
+        }
+        __align__(16) __half o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(v[j]);
+        *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = *reinterpret_cast<uint4*>(o);
+      }
+    }
+    cluster.sync();  // peers may still be reading this CTA's tile
   }
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kDqWarps + 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)C::kTmemCols)
                  : "memory");
   }
 }
@@ -355,9 +450,10 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN>
-int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, cudaStream_t stream) {
-  using C = TcCfg<BN>;
+template <int BN, int MT>
+int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, int Z,
+              cudaStream_t stream) {
+  using C = TcCfg<BN, MT>;
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return AWQ_B200_ERR_DRIVER;
   CUtensorMap map_x, map_w;
@@ -385,15 +481,30 @@ int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, cudaS
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  auto kernel = gemm_tc_kernel<BN, MT>;
   if (!attr_done[dev]) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::kSmemBytes) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
   }
-  dim3 grid((p.M + kBM - 1) / kBM, (p.N + BN - 1) / BN, 1);
-  gemm_tc_kernel<BN><<<grid, kTcThreads, C::kSmemBytes, stream>>>(map_x, map_w, p);
-  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.M + kBM * MT - 1) / (kBM * MT), (p.N + BN - 1) / BN, Z);
+  cfg.blockDim = dim3(kTcThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = Z;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, map_x, map_w, p) != cudaSuccess) {
+    cudaGetLastError();
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
 }
 
 }  // namespace
@@ -412,10 +523,23 @@ int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scale
                    int group, void*, size_t, cudaStream_t stream) {
   if (!gemm_tc_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
   TcParams p{scales, qzeros, bias, out, M, N, K, group};
-  // 128-column tiles when 256-column tiles would leave most SMs idle
-  const long tiles256 = (long)((M + kBM - 1) / kBM) * ((N + 255) / 256);
-  if (tiles256 < sm_count()) return launch_tc<128>(x, qweight, p, stream);
-  return launch_tc<256>(x, qweight, p, stream);
+  const int sms = sm_count();
+  const int KT = K / kBKtc;
+  auto tiles = [&](int bn, int mt) {
+    return (long)((M + kBM * mt - 1) / (kBM * mt)) * ((N + bn - 1) / bn);
+  };
+  // Preference: the 256-row tile (one dequantised B tile feeds two MMAs) when it fills the GPU;
+  // otherwise single-tile CTAs with K split across a cluster until about every SM has work.
+  if (M > kBM && tiles(256, 2) * 10 >= (long)sms * 8) return launch_tc<256, 2>(x, qweight, p, 1, stream);
+  auto split = [&](long t) {
+    long z = t > 0 ? sms / t : 1;
+    z = z < 1 ? 1 : (z > 8 ? 8 : z);
+    while (z > 1 && KT / z < 4) --z;
+    return (int)z;
+  };
+  const long t256 = tiles(256, 1);
+  if (N >= 256 && t256 * 8 >= sms) return launch_tc<256, 1>(x, qweight, p, split(t256), stream);
+  return launch_tc<128, 1>(x, qweight, p, split(tiles(128, 1)), stream);
 }
 
 int tc_device_status(int* out) {
