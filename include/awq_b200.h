@@ -147,6 +147,39 @@ int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, co
                          int expert_parallel, int64_t sorted_capacity, void* workspace,
                          size_t workspace_bytes, void* stream);
 
+/*
+ * awq_b200_moe_experts with no scratch argument, for hosts that cannot obtain device memory at
+ * call time.  (No counterpart in the reference: its Python callers always allocate through
+ * torch.)  Examples: a serving engine that has already handed every free byte of HBM to its
+ * KV-cache pool, so a late cudaMalloc would fail; a C or FFI host that has no device allocator
+ * of its own and must not call the CUDA allocation routines from its request loop.
+ *
+ * The activation and per-pair buffers live in one array inside the library, in device memory,
+ * awq_b200_moe_static_scratch_bytes() = 16 MiB per GPU, reserved on every GPU that loads the
+ * library for as long as the process runs.  Inputs and the output are still the caller's.
+ * Arguments are those of awq_b200_moe_experts without workspace / workspace_bytes.
+ *
+ *  - A problem whose scratch need, awq_b200_moe_workspace_bytes(T, topk, E, H, I), exceeds the
+ *    16 MiB is refused with AWQ_B200_ERR_LIMIT (Qwen3-30B-A3B shapes fit up to about 300
+ *    tokens); use awq_b200_moe_experts with your own buffer for those.
+ *  - The call never allocates or frees device memory.  The first call on each GPU looks up the
+ *    array's device address (one cudaGetSymbolAddress, cached per GPU); make that first call
+ *    during start-up, before any stream capture.
+ *  - All calls on one GPU share the one array and it keeps the previous call's contents.  What
+ *    has to start from zero is cleared by the call itself.  Two calls that overlap on the GPU
+ *    (different streams, or a graph replay racing a direct call) corrupt each other: keep calls
+ *    on one GPU ordered.
+ */
+size_t awq_b200_moe_static_scratch_bytes(void);
+
+int awq_b200_moe_experts_static(const void* x, const void* w13_q, const void* w13_s,
+                                const void* w13_z, const void* w2_q, const void* w2_s,
+                                const void* w2_z, const float* topk_weights,
+                                const int32_t* sorted_ids, const int32_t* expert_ids,
+                                const int32_t* num_post_pad, void* out, int T, int topk, int E,
+                                int H, int I, int group, int block, int expert_parallel,
+                                int64_t sorted_capacity, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

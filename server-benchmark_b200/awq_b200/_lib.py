@@ -38,6 +38,9 @@ PROTOTYPES = {
     "awq_b200_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "awq_b200_moe_experts": (c_int, [c_void_p] * 7 + [c_void_p] * 4 + [c_void_p] +
                              [c_int] * 8 + [c_int64, c_void_p, c_size_t, c_void_p]),
+    "awq_b200_moe_static_scratch_bytes": (c_size_t, []),
+    "awq_b200_moe_experts_static": (c_int, [c_void_p] * 7 + [c_void_p] * 4 + [c_void_p] +
+                                    [c_int] * 8 + [c_int64, c_void_p]),
 }
 
 _lib = None

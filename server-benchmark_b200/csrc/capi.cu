@@ -215,4 +215,49 @@ int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, co
                                  static_cast<cudaStream_t>(stream));
 }
 
+size_t awq_b200_moe_static_scratch_bytes(void) { return awq::moe_static_scratch_bytes(); }
+
+int awq_b200_moe_experts_static(const void* x, const void* w13_q, const void* w13_s,
+                                const void* w13_z, const void* w2_q, const void* w2_s,
+                                const void* w2_z, const float* topk_weights,
+                                const int32_t* sorted_ids, const int32_t* expert_ids,
+                                const int32_t* num_post_pad, void* out, int T, int topk, int E,
+                                int H, int I, int group, int block, int expert_parallel,
+                                int64_t sorted_capacity, void* stream) {
+  if (T == 0) return AWQ_B200_OK;
+  if (!x || !w13_q || !w13_s || !w13_z || !w2_q || !w2_s || !w2_z || !topk_weights ||
+      !sorted_ids || !expert_ids || !num_post_pad || !out)
+    return AWQ_B200_ERR_NULL;
+  if (T < 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0 || block <= 0) return AWQ_B200_ERR_SHAPE;
+  if (group != 128 && group != 64 && group != 32) return AWQ_B200_ERR_GROUP;
+  if (!awq::moe_supported(H, I, group, block)) return AWQ_B200_ERR_SHAPE;
+  if ((int64_t)T * topk > (1 << 24)) return AWQ_B200_ERR_LIMIT;
+  if ((sorted_capacity + block - 1) / block > 65535) return AWQ_B200_ERR_LIMIT;
+  if (sorted_capacity < awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block))
+    return AWQ_B200_ERR_WORKSPACE;
+  // the built-in scratch has a fixed size: larger problems are refused, not truncated
+  if (awq::moe_workspace_bytes(T, topk, E, H, I) > awq::moe_static_scratch_bytes())
+    return AWQ_B200_ERR_LIMIT;
+  if (!aligned16(x) || !aligned16(w13_q) || !aligned16(w13_s) || !aligned16(w13_z) ||
+      !aligned16(w2_q) || !aligned16(w2_s) || !aligned16(w2_z) || !aligned16(out))
+    return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  awq::MoeArgs a{static_cast<const __half*>(x),
+                 static_cast<const uint32_t*>(w13_q),
+                 static_cast<const __half*>(w13_s),
+                 static_cast<const uint32_t*>(w13_z),
+                 static_cast<const uint32_t*>(w2_q),
+                 static_cast<const __half*>(w2_s),
+                 static_cast<const uint32_t*>(w2_z),
+                 topk_weights,
+                 sorted_ids,
+                 expert_ids,
+                 num_post_pad,
+                 static_cast<__half*>(out),
+                 T, topk, E, H, I, group, block,
+                 sorted_capacity,
+                 expert_parallel};
+  return awq::launch_moe_experts_static(a, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

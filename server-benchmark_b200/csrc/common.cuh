@@ -145,5 +145,7 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I);
 int moe_block_size(int T, int topk, int E);
 int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream);
+int launch_moe_experts_static(const MoeArgs& a, cudaStream_t stream);
+size_t moe_static_scratch_bytes();
 
 }  // namespace awq

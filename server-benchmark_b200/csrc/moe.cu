@@ -21,6 +21,11 @@
 
 namespace cg = cooperative_groups;
 
+// Scratch for awq_b200_moe_experts_static: 16 MiB of device memory per GPU, reserved when the
+// library is loaded on that GPU and kept until the process ends.
+constexpr size_t kMoeStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_moe_static_scratch[kMoeStaticScratchBytes];
+
 namespace awq {
 
 namespace {
@@ -517,5 +522,37 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
   }
   return AWQ_B200_OK;
 }
+
+// ---- expert GEMMs with the scratch held inside the library ------------------------------------
+//
+// Same work as launch_moe_experts, but the activation / per-pair buffers live in
+// g_moe_static_scratch, a fixed array in device memory that every GPU loading the library
+// reserves until the process exits.  Nothing is allocated at call time.
+//
+// g_moe_static_scratch is a device symbol: in host code its name is only a handle, not an
+// address a kernel could use, so the device address is looked up once per device with
+// cudaGetSymbolAddress (that device being current) and cached.  The lookup happens in the first
+// call on each device.
+int launch_moe_experts_static(const MoeArgs& a, cudaStream_t stream) {
+  const size_t need = moe_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
+  if (need > kMoeStaticScratchBytes) return AWQ_B200_ERR_LIMIT;
+  static void* scratch_addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  if (scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_moe_static_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return AWQ_B200_ERR_LAUNCH;
+    }
+    scratch_addr[dev] = ptr;
+  }
+  // The array still holds whatever the previous call left there.  Every row the kernels read is
+  // written earlier in the same call; the one region that must start at zero (per-pair outputs
+  // under expert parallelism) is cleared inside launch_moe_experts.
+  return launch_moe_experts(a, scratch_addr[dev], kMoeStaticScratchBytes, stream);
+}
+
+size_t moe_static_scratch_bytes() { return kMoeStaticScratchBytes; }
 
 }  // namespace awq
