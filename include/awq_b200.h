@@ -74,6 +74,8 @@ int awq_b200_dequantize(const void* qweight, const void* scales, const void* qze
 #define AWQ_B200_KERNEL_STREAM 2   /* small-M weight-streaming kernel (mma.sync, cluster split-K) */
 #define AWQ_B200_KERNEL_TCGEN05 3  /* large-M tcgen05/TMEM kernel with in-smem dequantisation */
 #define AWQ_B200_KERNEL_STREAM_EXACT 4 /* small-M kernel with the magic-number conversion */
+#define AWQ_B200_KERNEL_TS 5       /* M <= 16: registers -> TMEM weights, tcgen05.mma (A in TMEM) */
+#define AWQ_B200_KERNEL_TS_EXACT 6 /* the same with the magic-number conversion */
 
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel);
 
@@ -84,7 +86,7 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
 /*
  * Health word of the tcgen05 kernel on the current device.  Its mbarrier waits are bounded;
  * a wait that ran out records which one (1 producer, 2-3 MMA issuer, 4 dequantisation,
- * 5 epilogue) and the kernel tears down instead of hanging.  0 = no wait ever ran out.
+ * 5 epilogue; 11-15 the M <= 16 kernel) and the kernel tears down instead of hanging.  0 = no wait ever ran out.
  * Synchronises the device (a plain device-to-host copy).  No counterpart in the reference.
  */
 int awq_b200_device_status(int* status);

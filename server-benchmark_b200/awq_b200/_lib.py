@@ -18,6 +18,8 @@ KERNEL_GENERIC = 1
 KERNEL_STREAM = 2
 KERNEL_TCGEN05 = 3
 KERNEL_STREAM_EXACT = 4
+KERNEL_TS = 5
+KERNEL_TS_EXACT = 6
 
 # name -> (restype, argtypes); kept in step with include/awq_b200.h
 PROTOTYPES = {

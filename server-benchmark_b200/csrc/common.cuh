@@ -116,6 +116,12 @@ int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scale
 
 int tc_device_status(int* out);
 
+bool gemm_ts_supported(int M, int N, int K, int group);
+int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scales,
+                   const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
+                   int group, bool exact, cudaStream_t stream);
+int ts_device_status(int* out);
+
 int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                         int renormalize, float* topk_weights, int32_t* topk_ids,
                         int32_t* token_expert_indices, cudaStream_t stream);
