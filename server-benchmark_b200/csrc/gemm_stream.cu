@@ -28,7 +28,7 @@ struct StreamParams {
 };
 
 constexpr int min_blocks(int MT, int WG) {
-  return WG == 1 ? (MT == 1 ? 4 : (MT == 2 ? 3 : 2)) : (MT == 1 ? 2 : 1);
+  return WG == 1 ? (MT <= 2 ? 4 : 2) : (MT == 1 ? 2 : 1);
 }
 
 template <int MT, bool EXACT, int GROUP, int WG>
@@ -156,11 +156,11 @@ template <int MT, bool EXACT, int GROUP>
 int launch_split(const StreamParams& p, cudaStream_t stream) {
   const int slabs = (p.N + kBN - 1) / kBN;
   const int KT = p.K / kBK;
-  const int want = (MT == 1 ? 4 : 3) * sm_count();  // warp groups in flight
+  const int want = 4 * sm_count();  // warp groups in flight
   int S = want / slabs;
   S = S < 1 ? 1 : (S > 8 ? 8 : S);
   if (S > KT) S = KT;
-  const bool two = MT <= 2 && slabs * S * 2 <= want && KT >= 2 * S * 2;
+  const bool two = MT == 1 && slabs * S * 2 <= want && KT >= 2 * S * 2;
   if (two) return launch_variant<MT, EXACT, GROUP, 2>(p, S, stream);
   return launch_variant<MT, EXACT, GROUP, 1>(p, S, stream);
 }

@@ -45,11 +45,12 @@ constexpr int kThreads = 128;
 constexpr int kWStageBytes = kBK * (kBN / kPack) * 4;  // 16384
 constexpr int kXPitch = kBK + 16;                      // halves (row pitch = 8 words mod 32)
 constexpr int kRedPitch = kBN + 8;                     // floats
-constexpr int kStages = 3;
 constexpr int kGroupThreads = 128;  // one warp group
 
 template <int MT>
 struct Cfg {
+  // MT = 2 trades the third stage for a fourth resident CTA per SM (more warps to hide latency)
+  static constexpr int kStages = MT == 2 ? 2 : 3;
   static constexpr int kStageBytes = kWStageBytes + MT * 8 * kXPitch * 2;
   static constexpr int kPipeBytes = kStages * kStageBytes;
   static constexpr int kRedBytes = MT * 8 * kRedPitch * 4;
@@ -101,7 +102,7 @@ template <int MT, bool EXACT, int GROUP>
 __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_base, int tid,
                                          int wg, int st_begin, int nst, int group, int ngroups,
                                          float (&tot)[MT][4][4]) {
-  constexpr int STAGES = kStages;
+  constexpr int STAGES = Cfg<MT>::kStages;
   constexpr int STAGE = Cfg<MT>::kStageBytes;
   const int lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -176,15 +177,7 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
 
       float acc[MT][4][4];
       float xs[MT][4];
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) acc[mt][i][c] = 0.f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) xs[mt][c] = 0.f;
-      }
+      const float kZero4[4] = {0.f, 0.f, 0.f, 0.f};
 
       // EXACT: per-column zero registers, as (z, z) pairs matching the (k, k+1) pairs.
       __half2 zu[4], zv[4];
@@ -251,12 +244,19 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
             a[3] = sv1 & mask;
           }
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma16816(acc[mt][i], a, b0[mt], b1[mt], acc[mt][i]);
+          for (int mt = 0; mt < MT; ++mt) {
+            // first step of a group starts from zero: no accumulator initialisation needed
+            if (s2 == 0) mma16816(acc[mt][i], a, b0[mt], b1[mt], kZero4);
+            else mma16816(acc[mt][i], a, b0[mt], b1[mt], acc[mt][i]);
+          }
         }
         if (!EXACT) {
           const uint32_t ones[4] = {0x00010001u, 0x00010001u, 0x00010001u, 0x00010001u};
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma16816(xs[mt], ones, b0[mt], b1[mt], xs[mt]);
+          for (int mt = 0; mt < MT; ++mt) {
+            if (s2 == 0) mma16816(xs[mt], ones, b0[mt], b1[mt], kZero4);
+            else mma16816(xs[mt], ones, b0[mt], b1[mt], xs[mt]);
+          }
         }
       }
 
@@ -265,14 +265,16 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 sf = __half22float2(as_half2(scw[i]));  // scales of columns 2i, 2i+1
-        float sa = sf.x, sb = sf.y, za = 0.f, zb = 0.f;
+        const float sa = sf.x, sb = sf.y;
+        float za = 0.f, zb = 0.f;
         if (!EXACT) {
-          const float fac = (i & 1) ? 1048576.f : 16777216.f;  // 2^20 : 2^24
-          const float zfac = (i & 1) ? 16.f : 1.f;
-          sa *= fac;
-          sb *= fac;
-          za = zfac * (float)((zw >> (4 * i)) & 0xF);
-          zb = zfac * (float)((zw >> (4 * i + 16)) & 0xF);
+          // zero nibbles -> float through the 2^23 mantissa trick (no int-to-float convert);
+          // odd i carry the factor 16 of the in-place nibble: take the zero as 16 z as well.
+          // The common factor 2^24 (2^20 for odd i) is applied once after the K loop.
+          const uint32_t zsa = (i & 1) ? (zw >> (4 * i - 4)) & 0xF0u : (zw >> (4 * i)) & 0xFu;
+          const uint32_t zsb = (i & 1) ? (zw >> (4 * i + 12)) & 0xF0u : (zw >> (4 * i + 16)) & 0xFu;
+          za = __uint_as_float(zsa | 0x4B000000u) - 8388608.f;
+          zb = __uint_as_float(zsb | 0x4B000000u) - 8388608.f;
         }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -290,6 +292,14 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
         }
       }
     }
+  }
+  if (!EXACT) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tot[mt][i][c] *= (i & 1) ? 1048576.f : 16777216.f;
   }
   cp_async_wait<0>();
   group_sync(wg);  // every warp of the group is done with the ring: the caller may reuse it
