@@ -36,7 +36,7 @@ PROTOTYPES = {
     "awq_b200_moe_sorted_capacity": (c_int64, [c_int64, c_int, c_int]),
     "awq_b200_moe_align_block_size": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                               c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
-    "awq_b200_moe_block_size": (c_int, [c_int, c_int, c_int]),
+    "awq_b200_moe_block_size": (c_int, [c_int] * 6),
     "awq_b200_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "awq_b200_moe_experts": (c_int, [c_void_p] * 7 + [c_void_p] * 4 + [c_void_p] +
                              [c_int] * 8 + [c_int64, c_void_p, c_size_t, c_void_p]),

@@ -224,7 +224,7 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
         return out
     lib = _lib.load()
     n_global = e if global_num_experts == -1 else global_num_experts
-    block = lib.awq_b200_moe_block_size(t, topk, n_global)
+    block = lib.awq_b200_moe_block_size(t, topk, n_global, h, inter, g)
     sorted_ids, expert_ids, num_post = moe_align_block_size(
         topk_ids, block, n_global, expert_map, ignore_invalid_experts=True)
     need = lib.awq_b200_moe_workspace_bytes(t, topk, n_global, h, inter)

@@ -175,7 +175,9 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
                                static_cast<cudaStream_t>(stream));
 }
 
-int awq_b200_moe_block_size(int T, int topk, int E) { return awq::moe_block_size(T, topk, E); }
+int awq_b200_moe_block_size(int T, int topk, int E, int H, int I, int group) {
+  return awq::moe_block_size(T, topk, E, H, I, group);
+}
 
 size_t awq_b200_moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   return awq::moe_workspace_bytes(T, topk, E, H, I);

@@ -454,9 +454,22 @@ int launch_moe_align(const int32_t* topk_ids, int numel, int E, int block,
   return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
 }
 
-int moe_block_size(int, int, int) { return 8 * kMoeMT; }
+int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H,
+                   cudaStream_t stream) {
+  const long long work = (long long)T * (H / 8);
+  moe_sum_kernel<<<(unsigned)((work + 255) / 256), 256, 0, stream>>>(pair_out, out, T, topk, H);
+  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
+// Row block of the permutation: 128 (tcgen05 grouped GEMMs) once an expert sees about 32 rows
+// or more on average and the shapes fit that kernel's tiles, otherwise 16 (streaming kernels).
+int moe_block_size(int T, int topk, int E, int H, int I, int group) {
+  const bool many_rows = (long long)T * topk >= 32LL * E;
+  return many_rows && moe_tc_supported(H, I, group) ? 128 : 8 * kMoeMT;
+}
 
 bool moe_supported(int H, int I, int group, int block) {
+  if (block == 128) return moe_tc_supported(H, I, group);
   // gate/up halves start on 16-byte boundaries (I % 32), stages are 128 rows of K
   return block == 8 * kMoeMT && H % kBK == 0 && I % kBK == 0 && I % 32 == 0 && H % 32 == 0 &&
          (group == 128 || group == 64 || group == 32);
@@ -464,15 +477,21 @@ bool moe_supported(int H, int I, int group, int block) {
 
 size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   if (T <= 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0) return 0;
-  const int block = moe_block_size(T, topk, E);
+  const int block = 8 * kMoeMT;
   const int64_t cap = awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block);
   const int64_t rows = (cap + block - 1) / block * block;
-  return align_up((size_t)rows * I * sizeof(__half), 256) +
-         align_up((size_t)T * topk * H * sizeof(__half), 256);
+  const size_t small = align_up((size_t)rows * I * sizeof(__half), 256) +
+                       align_up((size_t)T * topk * H * sizeof(__half), 256);
+  if (moe_block_size(T, topk, E, H, I, 128) == 128) {
+    const size_t big = moe_tc_workspace_bytes(T, topk, E, H, I);
+    return big > small ? big : small;
+  }
+  return small;
 }
 
 int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream) {
+  if (a.block == 128) return launch_moe_experts_tc(a, workspace, workspace_bytes, stream);
   const size_t need = moe_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
   if (workspace == nullptr || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
   const int numel = a.T * a.topk;

@@ -26,7 +26,7 @@ def _problem(lib, e, h, i, t, k, seed):
     x = synth.activations(t, h, seed=seed + 1).cuda()
     logits = synth.gating_logits(t, e, seed=seed + 2).cuda()
     wts, ids, _ = awq_b200.fused_topk(x, logits, k, True)
-    block = lib.awq_b200_moe_block_size(t, k, e)
+    block = lib.awq_b200_moe_block_size(t, k, e, h, i, 128)
     sorted_ids, expert_ids, num_post = awq_b200.moe_align_block_size(ids, block, e)
     return dict(x=x, w1=w1, w2=w2, wts=wts, sorted_ids=sorted_ids, expert_ids=expert_ids,
                 num_post=num_post, block=block, dims=(t, k, e, h, i))
