@@ -27,8 +27,17 @@ struct StreamParams {
   int M, N, K, group;
 };
 
+#ifndef AWQ_STREAM_BLOCKS_MT1
+#define AWQ_STREAM_BLOCKS_MT1 5
+#endif
+#ifndef AWQ_STREAM_MIN_STAGES
+#define AWQ_STREAM_MIN_STAGES 6
+#endif
+#ifndef AWQ_STREAM_MAX_CLUSTER
+#define AWQ_STREAM_MAX_CLUSTER 8
+#endif
 constexpr int min_blocks(int MT, int WG) {
-  return WG == 1 ? (MT <= 2 ? 4 : 2) : (MT == 1 ? 2 : 1);
+  return WG == 1 ? (MT == 1 ? AWQ_STREAM_BLOCKS_MT1 : (MT == 2 ? 4 : 2)) : (MT == 1 && WG <= 3 ? 2 : 1);
 }
 
 template <int MT, bool EXACT, int GROUP, int WG>
@@ -127,6 +136,10 @@ int launch_variant(const StreamParams& p, int S, cudaStream_t stream) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
+    if (AWQ_STREAM_MAX_CLUSTER > 8 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+            cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
   }
   const int slabs = (p.N + kBN - 1) / kBN;
@@ -156,12 +169,19 @@ template <int MT, bool EXACT, int GROUP>
 int launch_split(const StreamParams& p, cudaStream_t stream) {
   const int slabs = (p.N + kBN - 1) / kBN;
   const int KT = p.K / kBK;
-  const int want = 4 * sm_count();  // warp groups in flight
+  const int want = (MT == 1 ? AWQ_STREAM_BLOCKS_MT1 : 4) * sm_count();  // warp groups in flight
   int S = want / slabs;
-  S = S < 1 ? 1 : (S > 8 ? 8 : S);
-  if (S > KT) S = KT;
-  const bool two = MT == 1 && slabs * S * 2 <= want && KT >= 2 * S * 2;
-  if (two) return launch_variant<MT, EXACT, GROUP, 2>(p, S, stream);
+  S = S < 1 ? 1 : (S > AWQ_STREAM_MAX_CLUSTER ? AWQ_STREAM_MAX_CLUSTER : S);
+  while (S > 1 && KT / S < 3) --S;
+  // more warp groups per CTA when the cluster limit (8) leaves SMs under-filled
+  int wg = 1;
+  if (MT == 1) {
+    wg = want / (slabs * S);
+    wg = wg < 1 ? 1 : (wg > 3 ? 3 : wg);
+    while (wg > 1 && KT / (S * wg) < AWQ_STREAM_MIN_STAGES) --wg;
+  }
+  if (wg == 3) return launch_variant<MT, EXACT, GROUP, 3>(p, S, stream);
+  if (wg == 2) return launch_variant<MT, EXACT, GROUP, 2>(p, S, stream);
   return launch_variant<MT, EXACT, GROUP, 1>(p, S, stream);
 }
 
