@@ -65,6 +65,15 @@ def all_bytes_per_step(m: int) -> int:
     return tot
 
 
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -283,6 +292,13 @@ def run_cuda(args):
         if rank == 0:
             sampler.stop()
 
+        # ---- BASELINE configs 2 and 3 (1 GPU only): shape sweep and MoE layer ----
+        sweep = moe = None
+        if world == 1 and not args.no_sweep:
+            del graph
+            sweep = run_sweep(dev, stream)
+            moe = run_moe(dev, stream)
+
         # ---- tensor-parallel variant (N > 1): column/row shards + all-reduce ----
         tp_result = None
         if world > 1:
@@ -330,10 +346,93 @@ def run_cuda(args):
         }
         if tp_result is not None:
             line["tp"] = tp_result
+        if sweep is not None:
+            tpeak = measured_tensor_peak()
+            big = max((r for r in sweep if r["M"] >= 1024), key=lambda r: r["TFLOPs"])
+            line["roofline_tensor"] = {"bound": "tensor", "achieved": big["TFLOPs"],
+                                       "peak": tpeak[0], "unit": "TFLOP/s",
+                                       "frac": big["TFLOPs"] / tpeak[0], "peak_kind": f"of {tpeak[1]}",
+                                       "kernel": "gemm_tc_kernel<256,2>",
+                                       "point": {"shape": big["shape"], "M": big["M"]}}
+            line["sweep"] = sweep
+            line["moe"] = moe
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def graph_time(fns, stream, reps=3):
+    """Seconds per call of the callables in `fns` (each enqueues one op): captured once in a CUDA
+    graph, replayed `reps` times, CUDA events on `stream`."""
+    import torch
+    with torch.cuda.stream(stream):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / (reps * len(fns))
+
+
+def run_sweep(dev, stream):
+    """BASELINE config 2: the four 72B layer shapes x M in {1 .. 4096}, 1 GPU.  Weights are
+    rotated over enough copies that every launch reads more than the L2 holds."""
+    import torch
+    import awq_b200
+    from awq_b200 import synth
+    out = []
+    for name, (k, n) in shapes():
+        wbytes = k * n // 2
+        copies = max(1, -(-200_000_000 // wbytes))
+        base = [a.to(dev) for a in synth.awq_linear_tensors(k, n, GROUP, seed=1)]
+        sets = [base] + [[a.clone() for a in base] for _ in range(copies - 1)]
+        for m in synth.SWEEP_M:
+            x = synth.activations(m, k).to(dev)
+            fns = [(lambda q=q: awq_b200.awq_gemm(x, q[0], q[1], q[2], 8)) for q in sets]
+            t = graph_time(fns, stream, reps=3 if m >= 1024 else 10)
+            out.append({"shape": name, "K": k, "N": n, "M": m, "us": round(t * 1e6, 2),
+                        "weight_GBps": round(wbytes / t / 1e9, 1),
+                        "TFLOPs": round(2.0 * m * k * n / t / 1e12, 2)})
+        del sets, base
+    return out
+
+
+def run_moe(dev, stream):
+    """BASELINE config 3: Qwen3-30B-A3B fused-MoE layer (router -> permutation -> expert GEMMs ->
+    sum), T in {1 .. 4096}, 1 GPU."""
+    import torch
+    import awq_b200
+    from awq_b200 import synth
+    cfg = synth.QWEN3_MOE
+    e, h, i, k = cfg["experts"], cfg["hidden"], cfg["intermediate"], cfg["topk"]
+    w1, w2 = synth.moe_layer_tensors(e, h, i, GROUP)
+    w1 = tuple(a.to(dev) for a in w1)
+    w2 = tuple(a.to(dev) for a in w2)
+    out = []
+    for t in synth.MOE_TOKENS:
+        x = synth.activations(t, h).to(dev)
+        logits = synth.gating_logits(t, e).to(dev)
+        _, ids, _ = awq_b200.fused_topk(x, logits, k, True)
+        hit = int(torch.unique(ids).numel())
+        sec = graph_time([lambda: awq_b200.fused_moe(x, w1, w2, logits, k, True)], stream,
+                         reps=5 if t >= 1024 else 20)
+        byts = hit * (2359296 + 73728 + 18432) + t * h * 2 * 2
+        out.append({"T": t, "experts_hit": hit, "us": round(sec * 1e6, 1),
+                    "GBps": round(byts / sec / 1e9, 1),
+                    "TFLOPs": round(t * 75497472 / sec / 1e12, 2)})
+    return out
 
 
 def run_tp(args, world, rank, dev, stream, barrier):
@@ -444,6 +543,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="skip the shape sweep and the MoE layer (extra keys of the 1-GPU line)")
     args = ap.parse_args()
     if args.case:
         run_case(args)
