@@ -13,13 +13,20 @@
 //            MT = 2 one dequantised tile feeds two MMAs, halving the conversion work per flop.
 //   The packed weights [64 x BN/8 words] arrive by TMA (no swizzle) next to A.
 //
-// Warp roles (320 threads):
-//   warps 0-7  dequantise: one packed word -> 8 fp16 -> one 16-byte store; afterwards the
-//              epilogue: tcgen05.ld of their TMEM lane quarter, fp16 conversion, global stores.
-//   warp 8     TMA producer (one elected lane).
-//   warp 9     TMEM allocation; one elected lane issues tcgen05.mma and tcgen05.commit.
-// mbarrier rings: full_raw[s] (TMA landed) -> full_b[s] (B tile written) -> empty[s]
-// (tcgen05.commit: the MMAs that read stage s have finished), and tmem_full for the epilogue.
+// Warp roles (608 threads):
+//   warps 0-15 dequantise (two teams of 8 warps on alternate stages): one packed word -> 8 fp16
+//              -> one 16-byte store; afterwards the epilogue: tcgen05.ld of their TMEM lane
+//              quarter, fp16 conversion, global stores.
+//   warp 16    TMA producer of the packed weights (one elected lane), own ring of 4-8 slots.
+//   warp 17    TMEM allocation; one elected lane issues tcgen05.mma and tcgen05.commit.
+//   warp 18    TMA producer of the x tiles (one elected lane).
+// Barriers: raw_full / raw_empty per packed-weight slot; per x+B slot one `full` barrier (the
+// conversion threads' arrivals plus the x tile's TMA byte count) and one `empty` barrier
+// (tcgen05.commit), so the MMA thread waits once and commits once per stage -- tcgen05.mma issue is
+// paced by execution, and whatever else that thread does is a bubble in the tensor pipe.  A
+// packed-weight slot is released only after its words have been consumed by the conversion (an
+// issued shared-memory load is not yet a performed one).  tmem_full hands the accumulators to
+// the epilogue.
 //
 // Split-K (MT = 1 only): the Z CTAs of a thread-block cluster take consecutive K ranges of the
 // same tile; their fp32 accumulators are spilled to shared memory and summed through
@@ -41,21 +48,37 @@ using namespace tc;
 
 constexpr int kBM = 128;
 constexpr int kBKtc = 64;
-constexpr int kDqWarps = 8;
+constexpr int kDqWarps = 16;
 constexpr int kDqThreads = kDqWarps * 32;
-constexpr int kTcThreads = kDqThreads + 64;
+// The conversion warps form two teams that take alternate stages, so that one team's barrier
+// waits and dependency chains overlap with the other team's work.
+constexpr int kTeams = 2;
+constexpr int kTeamThreads = kDqThreads / kTeams;
+constexpr int kTcThreads = kDqThreads + 96;  // + raw producer, MMA issuer, A producer warps
 
+// Three rings with their own depths, because their producers have very different latencies:
+//   raw  packed weights from HBM (8 KB / stage)  -> deep, to keep enough bytes in flight
+//   A    x tiles, mostly L2 hits (16 KB per 128 rows / stage)
+//   B    dequantised tile handed from the conversion warps to the MMA (double buffer)
 template <int BN, int MT>
 struct TcCfg {
   static constexpr int kABytes = MT * kBM * kBKtc * 2;        // 16384 per 128-row tile
   static constexpr int kBBytes = kBKtc * BN * 2;              // 32768 / 16384
   static constexpr int kRawBytes = kBKtc * (BN / kPack) * 4;  // 8192 / 4096
-  static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
-  static constexpr int kStages = (BN == 256) ? 3 : (MT == 2 ? 4 : 5);
-  static constexpr int kBarBytes = 256;
+  // The hand-off latencies (conversion of a stage, MMA, commit -> barrier -> wake-up) add up to
+  // about three stage times, so the B ring must hold 3-4 stages for the tensor core to stay busy.
+  // x tile and dequantised tile of a stage share one full / one empty barrier, so the MMA
+  // thread waits once and commits once per stage; the packed weights have their own deeper ring.
+  static constexpr int kNA = BN == 128 ? 5 : (MT == 2 ? 3 : 4);
+  static constexpr int kNB = kNA;
+  static constexpr int kNR = BN == 128 ? 8 : (MT == 2 ? 4 : 4);
+  static constexpr int kAOff = 0;
+  static constexpr int kBOff = kNA * kABytes;
+  static constexpr int kRawOff = kBOff + kNB * kBBytes;
+  static constexpr int kPipeBytes = kRawOff + kNR * kRawBytes;
+  static constexpr int kBarBytes = 512;
   static constexpr int kRedPitch = BN + 4;  // floats, split-K spill tile
   static constexpr int kRedBytes = kBM * kRedPitch * 4;
-  static constexpr int kPipeBytes = kStages * kStageBytes;
   static constexpr int kMainBytes = kPipeBytes > kRedBytes ? kPipeBytes : kRedBytes;
   static constexpr int kSmemBytes = kMainBytes + kBarBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = BN * MT;
@@ -74,9 +97,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const TcParams p) {
   using C = TcCfg<BN, MT>;
-  constexpr int STAGES = C::kStages;
+  constexpr int NA = C::kNA, NB = C::kNB, NR = C::kNR;
   constexpr int WPR = BN / kPack;             // packed words per weight row of the tile
-  constexpr int KSTEP = kDqThreads / WPR;     // rows covered by the dequant threads per pass
+  constexpr int KSTEP = kTeamThreads / WPR;   // rows covered by one team per pass
   constexpr int PASSES = kBKtc / KSTEP;
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int s_abort;
@@ -88,13 +111,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + C::kMainBytes;
-  auto a_addr = [&](int s) { return smem_base + s * C::kStageBytes; };
-  auto b_addr = [&](int s) { return smem_base + s * C::kStageBytes + C::kABytes; };
-  auto raw_addr = [&](int s) { return smem_base + s * C::kStageBytes + C::kABytes + C::kBBytes; };
-  auto full_raw = [&](int s) { return bar_base + 8 * s; };
-  auto full_b = [&](int s) { return bar_base + 8 * (STAGES + s); };
-  auto empty = [&](int s) { return bar_base + 8 * (2 * STAGES + s); };
-  const uint32_t tmem_full = bar_base + 8 * (3 * STAGES);
+  auto a_addr = [&](int s) { return smem_base + C::kAOff + s * C::kABytes; };
+  auto b_addr = [&](int s) { return smem_base + C::kBOff + s * C::kBBytes; };
+  auto raw_addr = [&](int s) { return smem_base + C::kRawOff + s * C::kRawBytes; };
+  auto raw_full = [&](int s) { return bar_base + 8 * s; };
+  auto raw_empty = [&](int s) { return bar_base + 8 * (NR + s); };
+  // full[s]: kTeamThreads arrivals (B tile written) + 1 arrival with the x tile's byte count
+  auto full = [&](int s) { return bar_base + 8 * (2 * NR + s); };
+  auto empty = [&](int s) { return bar_base + 8 * (2 * NR + NA + s); };
+  const uint32_t tmem_full = bar_base + 8 * (2 * NR + 2 * NA);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.x * (kBM * MT);
@@ -107,9 +132,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_raw(s), 1);
-      mbar_init(full_b(s), kDqThreads);
+    for (int s = 0; s < NR; ++s) {
+      mbar_init(raw_full(s), 1);
+      mbar_init(raw_empty(s), kTeamThreads);
+    }
+    for (int s = 0; s < NA; ++s) {
+      mbar_init(full(s), kTeamThreads + 1);
       mbar_init(empty(s), 1);
     }
     mbar_init(tmem_full, 1);
@@ -130,18 +158,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   bool ok = true;
 
   if (warp == kDqWarps) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ packed-weight producer
     if (lane == 0) {
       for (int it = 0; it < KT; ++it) {
-        const int s = it % STAGES;
-        const uint32_t round = (uint32_t)(it / STAGES);
-        if (!mbar_wait(empty(s), (round & 1u) ^ 1u, &s_abort, 1)) break;
+        const int s = it % NR;
+        const uint32_t round = (uint32_t)(it / NR);
+        if (!mbar_wait(raw_empty(s), (round & 1u) ^ 1u, &s_abort, 1)) break;
+        mbar_arrive_expect_tx(raw_full(s), C::kRawBytes);
+        tma_load_2d(raw_addr(s), &map_w, n0 / kPack, (kt_begin + it) * kBKtc, raw_full(s));
+      }
+    }
+  } else if (warp == kDqWarps + 2) {
+    // ------------------------------------------------------------------ activation producer
+    if (lane == 0) {
+      for (int it = 0; it < KT; ++it) {
+        const int s = it % NA;
+        const uint32_t round = (uint32_t)(it / NA);
+        if (!mbar_wait(empty(s), (round & 1u) ^ 1u, &s_abort, 6)) break;
         const int k0 = (kt_begin + it) * kBKtc;
-        mbar_arrive_expect_tx(full_raw(s), C::kABytes + C::kRawBytes);
+        mbar_arrive_expect_tx(full(s), C::kABytes);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(a_addr(s) + mt * (kBM * kBKtc * 2), &map_x, k0, m0 + mt * kBM, full_raw(s));
-        tma_load_2d(raw_addr(s), &map_w, n0 / kPack, k0, full_raw(s));
+          tma_load_2d(a_addr(s) + mt * (kBM * kBKtc * 2), &map_x, k0, m0 + mt * kBM, full(s));
       }
     }
   } else if (warp == kDqWarps + 1) {
@@ -150,34 +188,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       // instruction descriptor: D fp32, A/B fp16, A K-major, B MN-major, N = BN, M = 128
       constexpr uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
                                  ((uint32_t)(kBM >> 4) << 24);
-      for (int it = 0; it < KT && ok; ++it) {
-        const int s = it % STAGES;
-        const uint32_t round = (uint32_t)(it / STAGES);
-        ok = mbar_wait(full_raw(s), round & 1u, &s_abort, 2) &&
-             mbar_wait(full_b(s), round & 1u, &s_abort, 3);
-        if (!ok) break;
-        tc_fence_after();
+      // descriptors of every ring slot, built once
+      uint64_t da[NA][MT], db[NA];
+#pragma unroll
+      for (int s = 0; s < NA; ++s) {
         // A: K-major SW128, 8-row core blocks 1024 B apart; B: MN-major SW128, 64-column
         // blocks 8192 B apart (LBO), 8-row k blocks 1024 B apart (SBO).
-        const uint64_t db = make_desc(b_addr(s), 8192, 1024);
+        db[s] = make_desc(b_addr(s), 8192, 1024);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const uint64_t da = make_desc(a_addr(s) + mt * (kBM * kBKtc * 2), 16, 1024);
+        for (int mt = 0; mt < MT; ++mt)
+          da[s][mt] = make_desc(a_addr(s) + mt * (kBM * kBKtc * 2), 16, 1024);
+      }
+      // tcgen05.mma issue is paced by execution, so everything else this thread does per stage
+      // is a bubble in the tensor pipe.  The wait for the next stage is therefore done before
+      // the last MMA of the current one is issued (it then overlaps with a running MMA).
+      int s = 0;
+      uint32_t phase = 0;
+      ok = KT == 0 || mbar_wait(full(0), 0, &s_abort, 2);
+      for (int it = 0; it < KT && ok; ++it) {
+        tc_fence_after();
+        int sn = s + 1;
+        uint32_t phase_n = phase;
+        if (sn == NA) { sn = 0; phase_n ^= 1u; }
 #pragma unroll
-          for (int k16 = 0; k16 < kBKtc / 16; ++k16) {
-            // advance 16 k: +32 B inside A's 128-byte rows, +16 rows (2048 B) in B
-            umma_f16_ss(tmem_d + mt * BN, da + (uint64_t)((k16 * 32) >> 4),
-                        db + (uint64_t)((k16 * 2048) >> 4), idesc, (it > 0 || k16 > 0) ? 1u : 0u);
+        for (int ss = 0; ss < NA; ++ss) {
+          if (ss != s) continue;  // compile-time slot index keeps the descriptors in registers
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int k16 = 0; k16 < kBKtc / 16; ++k16) {
+              if (mt == MT - 1 && k16 == kBKtc / 16 - 1 && it + 1 < KT) {
+                ok = mbar_wait(full(sn), phase_n, &s_abort, 2);
+              }
+              // advance 16 k: +32 B inside A's 128-byte rows, +16 rows (2048 B) in B
+              umma_f16_ss(tmem_d + mt * BN, da[ss][mt] + (uint64_t)((k16 * 32) >> 4),
+                          db[ss] + (uint64_t)((k16 * 2048) >> 4), idesc,
+                          (it > 0 || k16 > 0) ? 1u : 0u);
+            }
           }
         }
         umma_commit(empty(s));
+        s = sn;
+        phase = phase_n;
       }
       if (ok) umma_commit(tmem_full);
     }
-  } else {
+  } else if (warp < kDqWarps) {
     // ------------------------------------------------------------------ dequant warps
-    const int c = tid % WPR;            // packed word column inside the tile
-    const int krow0 = tid / WPR;
+    const int team = tid / kTeamThreads, tt = tid % kTeamThreads;
+    const int c = tt % WPR;             // packed word column inside the tile
+    const int krow0 = tt / WPR;
     const int wcol = min(n0 / kPack + c, words - 1);  // clamped past the N edge
     // KSTEP is a multiple of 8, so (k & 7) is the same for every row this thread converts
     const uint32_t b_off = (uint32_t)(c / 8) * (kBKtc * 128) + krow0 * 128 +
@@ -185,14 +245,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const uint32_t raw_off = (uint32_t)(krow0 * WPR + c) * 4;
     int cur_group = -1;
     __half2 zE0, zO0, zE1, zO1, sE0, sO0, sE1, sO1;
-    for (int it = 0; it < KT && ok; ++it) {
-      const int s = it % STAGES;
-      const uint32_t round = (uint32_t)(it / STAGES);
+    // scales / zeros are fetched one group ahead so that their L2 latency hides behind a group
+    const int ngroups = p.K / p.group;
+    const int g_first = min(((kt_begin + team) * kBKtc) / p.group, ngroups - 1);
+    uint32_t zw_n = __ldg(p.qzeros + (size_t)g_first * words + wcol);
+    uint4 sv_n = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g_first * p.N) + wcol);
+    for (int it = team; it < KT && ok; it += kTeams) {
+      const int sr = it % NR, sb = it % NA;
       const int grp = ((kt_begin + it) * kBKtc) / p.group;
       if (grp != cur_group) {
         cur_group = grp;
-        const uint32_t zw = __ldg(p.qzeros + (size_t)grp * words + wcol);
-        const uint4 sv = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)grp * p.N) + wcol);
+        const uint32_t zw = zw_n;
+        const uint4 sv = sv_n;
+        // prefetch for the next stage of this team that lies in a different group
+        int itn = it + kTeams;
+        while (itn < KT && ((kt_begin + itn) * kBKtc) / p.group == grp) itn += kTeams;
+        const int gn = min(((kt_begin + itn) * kBKtc) / p.group, ngroups - 1);
+        zw_n = __ldg(p.qzeros + (size_t)gn * words + wcol);
+        sv_n = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)gn * p.N) + wcol);
         const uint32_t zw8 = zw >> 8;
         zE0 = as_half2(lop3_and_or(zw, 0x000F000Fu, 0x64006400u));   // 1024 + z, cols 0,1
         zO0 = as_half2(lop3_and_or(zw, 0x00F000F0u, 0x64006400u));   // 1024 + 16 z, cols 2,3
@@ -204,13 +274,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         sE1 = as_half2(sv.z);
         sO1 = __hmul2(as_half2(sv.w), r16);
       }
-      ok = mbar_wait(full_raw(s), round & 1u, &s_abort, 4);
+      ok = mbar_wait(raw_full(sr), (uint32_t)((it / NR) & 1), &s_abort, 4);
       if (!ok) break;
-      const uint32_t raw = raw_addr(s) + raw_off, bt = b_addr(s) + b_off;
+      const uint32_t raw = raw_addr(sr) + raw_off, bt = b_addr(sb) + b_off;
       uint32_t w[PASSES];
 #pragma unroll
       for (int j = 0; j < PASSES; ++j)
         asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[j]) : "r"(raw + j * (KSTEP * WPR * 4)));
+      // the B slot was last read by the MMAs of stage it - NB
+      ok = mbar_wait(empty(sb), (uint32_t)(((it / NA) & 1) ^ 1), &s_abort, 7);
+      if (!ok) break;
 #pragma unroll
       for (int j = 0; j < PASSES; ++j) {
         const uint32_t w8 = w[j] >> 8;
@@ -223,17 +296,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                      "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
                      : "memory");
       }
+      mbar_arrive(raw_empty(sr));  // every packed word of the slot has been consumed
       fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
-      mbar_arrive(full_b(s));
+      mbar_arrive(full(sb));
     }
 
     // ---------------------------------------------------------------- epilogue
     // warp w reads TMEM lanes 32 (w % 4) ..; with MT = 2 warps 4-7 own the second accumulator,
     // with MT = 1 they own the upper half of the columns.
+    // sixteen warps: four per lane quarter, each taking a quarter of that quarter's columns
+    constexpr int kSlices = kDqWarps / 4;  // warps per lane quarter
     const int q = warp & 3, hi = warp >> 2;
-    const int acc = MT == 2 ? hi : 0;
-    const int col_begin = MT == 2 ? 0 : hi * (BN / 2);
-    const int col_end = MT == 2 ? BN : (hi + 1) * (BN / 2);
+    const int acc = MT == 2 ? hi / (kSlices / 2) : 0;
+    const int cols_per = MT == 2 ? BN / (kSlices / 2) : BN / kSlices;
+    const int col_begin = (MT == 2 ? hi % (kSlices / 2) : hi) * cols_per;
+    const int col_end = col_begin + cols_per;
     const uint32_t tlane = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
     if (KT > 0) ok = ok && mbar_wait(tmem_full, 0, &s_abort, 5);
     if (ok && Z == 1) {
@@ -263,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
     } else if (ok && MT == 1) {
-      // split-K: spill this CTA's fp32 partial tile to shared memory (the ring is idle now)
+      // split-K: spill this CTA's fp32 partial tile to shared memory (the rings are idle now)
       tc_fence_after();
       float* red = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
       const int row = q * 32 + lane;

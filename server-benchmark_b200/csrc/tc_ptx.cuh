@@ -41,9 +41,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false if the CTA has been aborted (by this thread or another).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;  // fast path: the phase is already complete
+  for (uint32_t i = 1; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
+    if ((i & 31u) == 0 && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(&g_tc_status, 0, code);
