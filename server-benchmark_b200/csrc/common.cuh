@@ -115,6 +115,11 @@ int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scale
                    int group, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 int tc_device_status(int* out);
+int launch_tc_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
+                      const __half* scales, const uint32_t* qzeros, const float* topk_weights,
+                      const int32_t* sorted_ids, const int32_t* expert_ids,
+                      const int32_t* num_post_pad, __half* out, int numel, int K, int N, int group,
+                      int half_cols, int nblk, cudaStream_t stream);
 
 bool gemm_ts_supported(int M, int N, int K, int group);
 int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scales,

@@ -90,20 +90,36 @@ struct TcParams {
   const __half* bias;
   __half* out;
   int M, N, K, group;
+  // grouped (MoE) modes only
+  const float* topk_weights;   // [T * topk]
+  const int32_t* sorted_ids;   // permuted (token, slot) list, padded to 128 per expert
+  const int32_t* expert_ids;   // expert of every 128-row block
+  const int32_t* num_post_pad;
+  int numel;                   // T * topk
+  int half_cols;               // gate_up: I (column offset of the up half)
 };
 
-template <int BN, int MT>
+// MODE 0: dense linear  y[M, N] = x @ W (+ bias).
+// MODE 1: grouped gate_up of a fused-MoE layer: row block b of the permuted list belongs to expert
+//         expert_ids[b]; the tile's 256 columns are 128 gate columns and the matching 128 up
+//         columns; epilogue silu(gate) * up -> act[pos] (N = 2I per expert).
+// MODE 2: grouped down projection: epilogue times routed weight -> pair_out[flat pair id].
+template <int BN, int MT, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const TcParams p) {
   using C = TcCfg<BN, MT>;
   constexpr int NA = C::kNA, NB = C::kNB, NR = C::kNR;
-  constexpr int WPR = BN / kPack;             // packed words per weight row of the tile
-  constexpr int KSTEP = kTeamThreads / WPR;   // rows covered by one team per pass
+  // the packed weights of a tile arrive as BN / 128 boxes of [64 rows x 16 words]
+  constexpr int HALVES = BN / 128;
+  constexpr int HALF_THREADS = kTeamThreads / HALVES;  // team threads converting one box
+  constexpr int KSTEP = HALF_THREADS / 16;    // rows covered per pass
   constexpr int PASSES = kBKtc / KSTEP;
+  static_assert(MODE == 0 || (BN == 256 && MT == 1), "grouped modes use 128 x 256 tiles");
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int s_abort;
   __shared__ uint32_t s_tmem_base;
+  __shared__ int s_fid[MODE == 2 ? kBM : 1];
 
   cg::cluster_group cluster = cg::this_cluster();
   const int zrank = (int)cluster.block_rank();
@@ -122,14 +138,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tmem_full = bar_base + 8 * (2 * NR + 2 * NA);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * (kBM * MT);
-  const int n0 = blockIdx.y * BN;
+  const int words = p.N / kPack;  // packed words per weight row (of one expert)
+  int m0, n0, w_left, w_right, wrow0 = 0;
+  const __half* scales = p.scales;
+  const uint32_t* qzeros = p.qzeros;
+  if (MODE == 0) {
+    m0 = blockIdx.x * (kBM * MT);
+    n0 = blockIdx.y * BN;
+    w_left = n0 / kPack;
+    w_right = w_left + 16;
+  } else {
+    m0 = blockIdx.x * kBM;  // position in the permuted list
+    // uniform over the CTA and before anything is allocated: unused blocks leave at once
+    if (m0 >= p.num_post_pad[0]) return;
+    const int e = p.expert_ids[blockIdx.x];
+    if (e < 0) return;
+    if (MODE == 1) {
+      n0 = blockIdx.y * 128;  // activation column of the tile
+      w_left = blockIdx.y * 16;
+      w_right = p.half_cols / kPack + blockIdx.y * 16;
+    } else {
+      n0 = blockIdx.y * BN;
+      w_left = n0 / kPack;
+      w_right = w_left + 16;
+    }
+    wrow0 = e * p.K;
+    const size_t groups = (size_t)(p.K / p.group);
+    scales += (size_t)e * groups * p.N;
+    qzeros += (size_t)e * groups * words;
+  }
   const int KT_all = p.K / kBKtc;
   const int kt_begin = (int)(((long long)zrank * KT_all) / Z);
   const int kt_end = (int)(((long long)(zrank + 1) * KT_all) / Z);
   const int KT = kt_end - kt_begin;
-  const int words = p.N / kPack;
 
+  if (MODE == 2 && tid < kBM) s_fid[tid] = p.sorted_ids[m0 + tid];
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < NR; ++s) {
@@ -165,7 +208,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const uint32_t round = (uint32_t)(it / NR);
         if (!mbar_wait(raw_empty(s), (round & 1u) ^ 1u, &s_abort, 1)) break;
         mbar_arrive_expect_tx(raw_full(s), C::kRawBytes);
-        tma_load_2d(raw_addr(s), &map_w, n0 / kPack, (kt_begin + it) * kBKtc, raw_full(s));
+        const int krow = wrow0 + (kt_begin + it) * kBKtc;
+        tma_load_2d(raw_addr(s), &map_w, w_left, krow, raw_full(s));
+        if (HALVES == 2) tma_load_2d(raw_addr(s) + 4096, &map_w, w_right, krow, raw_full(s));
       }
     }
   } else if (warp == kDqWarps + 2) {
@@ -236,20 +281,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   } else if (warp < kDqWarps) {
     // ------------------------------------------------------------------ dequant warps
     const int team = tid / kTeamThreads, tt = tid % kTeamThreads;
-    const int c = tt % WPR;             // packed word column inside the tile
-    const int krow0 = tt / WPR;
-    const int wcol = min(n0 / kPack + c, words - 1);  // clamped past the N edge
+    // inside a team: threads [0, HALF_THREADS) convert the left box, the rest the right box
+    const int half = tt / HALF_THREADS, th = tt % HALF_THREADS;
+    const int c16 = th & 15, krow0 = th >> 4;
+    const int c = half * 16 + c16;      // packed word column inside the tile
+    const int wcol = min((half ? w_right : w_left) + c16, words - 1);  // clamped past the N edge
     // KSTEP is a multiple of 8, so (k & 7) is the same for every row this thread converts
     const uint32_t b_off = (uint32_t)(c / 8) * (kBKtc * 128) + krow0 * 128 +
                            (((uint32_t)(c & 7) ^ (uint32_t)(krow0 & 7)) << 4);
-    const uint32_t raw_off = (uint32_t)(krow0 * WPR + c) * 4;
+    const uint32_t raw_off = (uint32_t)half * 4096 + (uint32_t)(krow0 * 16 + c16) * 4;
     int cur_group = -1;
     __half2 zE0, zO0, zE1, zO1, sE0, sO0, sE1, sO1;
     // scales / zeros are fetched one group ahead so that their L2 latency hides behind a group
     const int ngroups = p.K / p.group;
     const int g_first = min(((kt_begin + team) * kBKtc) / p.group, ngroups - 1);
-    uint32_t zw_n = __ldg(p.qzeros + (size_t)g_first * words + wcol);
-    uint4 sv_n = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g_first * p.N) + wcol);
+    uint32_t zw_n = __ldg(qzeros + (size_t)g_first * words + wcol);
+    uint4 sv_n = __ldg(reinterpret_cast<const uint4*>(scales + (size_t)g_first * p.N) + wcol);
     for (int it = team; it < KT && ok; it += kTeams) {
       const int sr = it % NR, sb = it % NA;
       const int grp = ((kt_begin + it) * kBKtc) / p.group;
@@ -261,8 +308,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         int itn = it + kTeams;
         while (itn < KT && ((kt_begin + itn) * kBKtc) / p.group == grp) itn += kTeams;
         const int gn = min(((kt_begin + itn) * kBKtc) / p.group, ngroups - 1);
-        zw_n = __ldg(p.qzeros + (size_t)gn * words + wcol);
-        sv_n = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)gn * p.N) + wcol);
+        zw_n = __ldg(qzeros + (size_t)gn * words + wcol);
+        sv_n = __ldg(reinterpret_cast<const uint4*>(scales + (size_t)gn * p.N) + wcol);
         const uint32_t zw8 = zw >> 8;
         zE0 = as_half2(lop3_and_or(zw, 0x000F000Fu, 0x64006400u));   // 1024 + z, cols 0,1
         zO0 = as_half2(lop3_and_or(zw, 0x00F000F0u, 0x64006400u));   // 1024 + 16 z, cols 2,3
@@ -280,7 +327,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       uint32_t w[PASSES];
 #pragma unroll
       for (int j = 0; j < PASSES; ++j)
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[j]) : "r"(raw + j * (KSTEP * WPR * 4)));
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[j]) : "r"(raw + j * (KSTEP * 16 * 4)));
       // the B slot was last read by the MMAs of stage it - NB
       ok = mbar_wait(empty(sb), (uint32_t)(((it / NA) & 1) ^ 1), &s_abort, 7);
       if (!ok) break;
@@ -313,7 +360,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int col_end = col_begin + cols_per;
     const uint32_t tlane = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
     if (KT > 0) ok = ok && mbar_wait(tmem_full, 0, &s_abort, 5);
-    if (ok && Z == 1) {
+    if (ok && MODE == 1) {
+      // act[pos, n0 + c] = silu(D[c]) * D[128 + c]; warp slice hi owns 32 of the 128 columns
+      tc_fence_after();
+      const int row = q * 32 + lane;
+      const int c0 = hi * 32;
+      uint32_t g[32], u[32];
+      tmem_ld32(tlane + (uint32_t)c0, g);
+      tmem_ld32(tlane + (uint32_t)(128 + c0), u);
+      if (n0 + c0 < p.half_cols) {
+        __align__(16) __half2 h[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+          h[j] = __floats2half2_rn(g0 / (1.f + __expf(-g0)) * __uint_as_float(u[2 * j]),
+                                   g1 / (1.f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]));
+        }
+        uint4* dst =
+            reinterpret_cast<uint4*>(p.out + (size_t)(m0 + row) * p.half_cols + n0 + c0);
+        const uint4* srcv = reinterpret_cast<const uint4*>(h);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = srcv[j];
+      }
+    } else if (ok && MODE == 2) {
+      // pair_out[fid, n0 + c] = routed weight * D[c]; warp slice hi owns 64 of the 256 columns
+      tc_fence_after();
+      const int fid = s_fid[q * 32 + lane];
+      const bool valid = fid < p.numel;
+      const float rw = valid ? __ldg(p.topk_weights + fid) : 0.f;
+#pragma unroll 1
+      for (int c0 = hi * 64; c0 < hi * 64 + 64; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tlane + (uint32_t)c0, r);
+        if (valid && n0 + c0 < p.N) {
+          __align__(16) __half2 h[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            h[j] = __floats2half2_rn(__uint_as_float(r[2 * j]) * rw,
+                                     __uint_as_float(r[2 * j + 1]) * rw);
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)fid * p.N + n0 + c0);
+          const uint4* srcv = reinterpret_cast<const uint4*>(h);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = srcv[j];
+        }
+      }
+    } else if (ok && Z == 1) {
       tc_fence_after();
       const int m = m0 + acc * kBM + q * 32 + lane;
 #pragma unroll 1
@@ -362,7 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   }
 
-  if (MT == 1 && Z > 1) {
+  if (MODE == 0 && MT == 1 && Z > 1) {
     // ---------------------------------------------------------------- cluster split-K reduce
     cluster.sync();
     if (!s_abort) {
@@ -431,38 +522,45 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, int MT>
-int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, int Z,
-              cudaStream_t stream) {
-  using C = TcCfg<BN, MT>;
+// fp16 activations [rows, cols], box [64 k x 128 rows], 128-byte swizzle
+int make_a_map(CUtensorMap* m, const __half* base, int64_t rows, int cols) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return AWQ_B200_ERR_DRIVER;
-  CUtensorMap map_x, map_w;
-  {
-    const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
-    const cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBKtc, (cuuint32_t)kBM};
-    const cuuint32_t estr[2] = {1, 1};
-    if (enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return AWQ_B200_ERR_DRIVER;
-  }
-  {
-    const cuuint64_t dims[2] = {(cuuint64_t)(p.N / kPack), (cuuint64_t)p.K};
-    const cuuint64_t strides[1] = {(cuuint64_t)(p.N / kPack) * 4};
-    const cuuint32_t box[2] = {(cuuint32_t)(BN / kPack), (cuuint32_t)kBKtc};
-    const cuuint32_t estr[2] = {1, 1};
-    if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<uint32_t*>(qweight), dims,
-            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return AWQ_B200_ERR_DRIVER;
-  }
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBKtc, (cuuint32_t)kBM};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+             ? AWQ_B200_OK
+             : AWQ_B200_ERR_DRIVER;
+}
+
+// packed weights [rows, words] (experts stacked along the rows), box [16 words x 64 rows]
+int make_w_map(CUtensorMap* m, const uint32_t* base, int64_t rows, int words) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return AWQ_B200_ERR_DRIVER;
+  const cuuint64_t dims[2] = {(cuuint64_t)words, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)words * 4};
+  const cuuint32_t box[2] = {16, (cuuint32_t)kBKtc};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<uint32_t*>(base), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+             ? AWQ_B200_OK
+             : AWQ_B200_ERR_DRIVER;
+}
+
+template <int BN, int MT, int MODE>
+int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const TcParams& p, dim3 grid,
+                  int Z, cudaStream_t stream) {
+  using C = TcCfg<BN, MT>;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
-  auto kernel = gemm_tc_kernel<BN, MT>;
+  auto kernel = gemm_tc_kernel<BN, MT, MODE>;
   if (!attr_done[dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::kSmemBytes) != cudaSuccess)
@@ -470,7 +568,7 @@ int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, int Z
     attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.M + kBM * MT - 1) / (kBM * MT), (p.N + BN - 1) / BN, Z);
+  cfg.gridDim = grid;
   cfg.blockDim = dim3(kTcThreads, 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
@@ -481,11 +579,21 @@ int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, int Z
   attr[0].val.clusterDim.z = Z;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, map_x, map_w, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, p) != cudaSuccess) {
     cudaGetLastError();
     return AWQ_B200_ERR_LAUNCH;
   }
   return AWQ_B200_OK;
+}
+
+template <int BN, int MT>
+int launch_tc(const __half* x, const uint32_t* qweight, const TcParams& p, int Z,
+              cudaStream_t stream) {
+  CUtensorMap map_x, map_w;
+  if (int rc = make_a_map(&map_x, x, p.M, p.K)) return rc;
+  if (int rc = make_w_map(&map_w, qweight, p.K, p.N / kPack)) return rc;
+  const dim3 grid((p.M + kBM * MT - 1) / (kBM * MT), (p.N + BN - 1) / BN, Z);
+  return launch_kernel<BN, MT, 0>(map_x, map_w, p, grid, Z, stream);
 }
 
 }  // namespace
@@ -503,7 +611,7 @@ int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scale
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, void*, size_t, cudaStream_t stream) {
   if (!gemm_tc_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
-  TcParams p{scales, qzeros, bias, out, M, N, K, group};
+  TcParams p{scales, qzeros, bias, out, M, N, K, group, nullptr, nullptr, nullptr, nullptr, 0, 0};
   const int sms = sm_count();
   const int KT = K / kBKtc;
   auto tiles = [&](int bn, int mt) {
@@ -521,6 +629,24 @@ int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scale
   const long t256 = tiles(256, 1);
   if (N >= 256 && t256 * 8 >= sms) return launch_tc<256, 1>(x, qweight, p, split(t256), stream);
   return launch_tc<128, 1>(x, qweight, p, split(tiles(128, 1)), stream);
+}
+
+// Grouped expert GEMM of a fused-MoE layer on the same pipeline (see the MODE comment of the
+// kernel).  a: activations in permuted row order [a_rows, K]; w: packed expert weights stacked
+// along the rows [E * K, N / 8].
+int launch_tc_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
+                      const __half* scales, const uint32_t* qzeros, const float* topk_weights,
+                      const int32_t* sorted_ids, const int32_t* expert_ids,
+                      const int32_t* num_post_pad, __half* out, int numel, int K, int N, int group,
+                      int half_cols, int nblk, cudaStream_t stream) {
+  CUtensorMap map_a, map_w;
+  if (int rc = make_a_map(&map_a, a, a_rows, K)) return rc;
+  if (int rc = make_w_map(&map_w, w, (int64_t)experts * K, N / kPack)) return rc;
+  TcParams p{scales, qzeros, nullptr, out, (int)a_rows, N, K, group, topk_weights, sorted_ids,
+             expert_ids, num_post_pad, numel, half_cols};
+  if (mode == 1)
+    return launch_kernel<256, 1, 1>(map_a, map_w, p, dim3(nblk, half_cols / 128, 1), 1, stream);
+  return launch_kernel<256, 1, 2>(map_a, map_w, p, dim3(nblk, N / 256, 1), 1, stream);
 }
 
 int tc_device_status(int* out) {
