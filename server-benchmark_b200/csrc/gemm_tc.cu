@@ -229,54 +229,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else if (warp == kDqWarps + 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop and stays converged; one elected lane issues.  (A lane that
+    // loops alone while the rest of its warp is parked pays several times more per tcgen05
+    // instruction, see elect_one in tc_ptx.cuh.)
+    {
       // instruction descriptor: D fp32, A/B fp16, A K-major, B MN-major, N = BN, M = 128
       constexpr uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
                                  ((uint32_t)(kBM >> 4) << 24);
+      // tcgen05 operands live in uniform registers: derive them from warp-uniform values only
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_d, 0);
       // descriptors of every ring slot, built once
       uint64_t da[NA][MT], db[NA];
 #pragma unroll
       for (int s = 0; s < NA; ++s) {
         // A: K-major SW128, 8-row core blocks 1024 B apart; B: MN-major SW128, 64-column
         // blocks 8192 B apart (LBO), 8-row k blocks 1024 B apart (SBO).
-        db[s] = make_desc(b_addr(s), 8192, 1024);
+        db[s] = make_desc(__shfl_sync(0xffffffffu, b_addr(s), 0), 8192, 1024);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          da[s][mt] = make_desc(a_addr(s) + mt * (kBM * kBKtc * 2), 16, 1024);
+          da[s][mt] = make_desc(
+              __shfl_sync(0xffffffffu, a_addr(s) + mt * (kBM * kBKtc * 2), 0), 16, 1024);
       }
-      // tcgen05.mma issue is paced by execution, so everything else this thread does per stage
-      // is a bubble in the tensor pipe.  The wait for the next stage is therefore done before
-      // the last MMA of the current one is issued (it then overlaps with a running MMA).
+      // The tensor pipe runs one MMA after the other, so whatever else this warp does between
+      // two of them is a bubble.  The wait for the next stage is therefore done before the last
+      // MMA of the current one is issued (it then overlaps with a running MMA).
       int s = 0;
       uint32_t phase = 0;
       ok = KT == 0 || mbar_wait(full(0), 0, &s_abort, 2);
+      ok = __all_sync(0xffffffffu, ok);
       for (int it = 0; it < KT && ok; ++it) {
         tc_fence_after();
         int sn = s + 1;
         uint32_t phase_n = phase;
         if (sn == NA) { sn = 0; phase_n ^= 1u; }
+        constexpr int kLast = MT * (kBKtc / 16) - 1;
+        auto issue = [&](int first, int last) {  // MMAs [first, last] of the stage
 #pragma unroll
-        for (int ss = 0; ss < NA; ++ss) {
-          if (ss != s) continue;  // compile-time slot index keeps the descriptors in registers
+          for (int ss = 0; ss < NA; ++ss) {
+            if (ss != s) continue;  // compile-time slot index keeps the descriptors in registers
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int k16 = 0; k16 < kBKtc / 16; ++k16) {
-              if (mt == MT - 1 && k16 == kBKtc / 16 - 1 && it + 1 < KT) {
-                ok = mbar_wait(full(sn), phase_n, &s_abort, 2);
-              }
+            for (int i = 0; i <= kLast; ++i) {
+              if (i < first || i > last) continue;
+              const int mt = i / (kBKtc / 16), k16 = i % (kBKtc / 16);
               // advance 16 k: +32 B inside A's 128-byte rows, +16 rows (2048 B) in B
-              umma_f16_ss(tmem_d + mt * BN, da[ss][mt] + (uint64_t)((k16 * 32) >> 4),
+              umma_f16_ss(tmem_u + mt * BN, da[ss][mt] + (uint64_t)((k16 * 32) >> 4),
                           db[ss] + (uint64_t)((k16 * 2048) >> 4), idesc,
                           (it > 0 || k16 > 0) ? 1u : 0u);
             }
           }
+        };
+        if (elect_one()) issue(0, kLast - 1);
+        __syncwarp();
+        if (it + 1 < KT) {
+          ok = mbar_wait(full(sn), phase_n, &s_abort, 2);
+          ok = __all_sync(0xffffffffu, ok);
         }
-        umma_commit(empty(s));
+        if (elect_one()) {
+          issue(kLast, kLast);
+          umma_commit(empty(s));
+        }
+        __syncwarp();
         s = sn;
         phase = phase_n;
       }
-      if (ok) umma_commit(tmem_full);
+      if (ok && elect_one()) umma_commit(tmem_full);
+      __syncwarp();
     }
   } else if (warp < kDqWarps) {
     // ------------------------------------------------------------------ dequant warps

@@ -9,27 +9,45 @@
 // B operand ([16 tokens x 64 k] K-major, 128-byte swizzle) in shared memory.  The dequantised
 // weights never touch shared memory and the 5th-generation tensor core does the arithmetic.
 //
-// CTA = 4 conversion warps + 1 control warp; slab of 256 output columns (two 128-lane A tiles);
-// K range split over a thread-block cluster as in gemm_stream.cu.  Per 128-row stage (one
-// quantisation group):
-//   conversion warps  cp.async ring (packed weights 16 KB + x 4 KB, 3 stages)
-//                     -> per 16-row step 4 x tcgen05.st (16 lanes x 8 columns each) into A buffer
-//                        h (h = half of the stage), then arrive on a_full[h]
-//   control thread    waits a_full[h]; 4 steps x (2 weight tiles + 1 constant tile) MMAs into the
-//                     group accumulators D[b]; tcgen05.commit -> a_empty[h]
-//   conversion warps  (one stage later) tcgen05.ld their lane of D[b] -> fold
-//                     tot += scale * (acc - zero * sum_x) in fp32 registers -> arrive d_empty[b]
+// The CTA is a pipeline of specialised warps joined by mbarrier rings (slab of 256 output
+// columns = two 128-lane A tiles; stage = 128 weight rows = one quantisation group; K range
+// split over a thread-block cluster as in gemm_stream.cu):
+//
+//   producer (1 thread)   TMA: packed weights [128 rows x 128 B] + x [16 tokens x 128 k] of a
+//                         stage into a 5-deep shared-memory ring            raw_full / raw_empty
+//   conversion (8 warps)  warp (q, p): TMEM lane quarter q, quarter-stages c = p and p + 2.
+//                         Per quarter-stage (two 16-row steps): ld.shared -> unpack ->
+//                         8 x tcgen05.st into A slot c                      a_full[c] / done0, done1
+//   issue (1 warp)        converged warp, one elected lane: per 16-row step one MMA per A tile
+//                         (weight tile 0, weight tile 1, constant tile) into the group
+//                         accumulators D[b]; two tcgen05.commit per stage   done0, done1[b] / d_empty[b]
+//   fold (4 warps)        warp q: tcgen05.ld its lanes of D[b];
+//                         tot += scale * (acc - zero * sum_x) in fp32 registers
+//
 // The constant tile (every k slot = 2^-24) yields sum_k x per token in the same scaling as the
 // weight tiles, so the zero point is applied per group without a separate reduction.
 //
-// TMEM columns (256 allocated): D[2 buffers][3 tiles][16] = 96, A[2 halves][2 tiles][32] = 128,
-// constant tile 8.  Lane l of quarter q (= conversion warp q) holds output column
-//   64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8      of the slab.
+// Measured on B200 while building this kernel (cycles of the SM clock):
+//   * a tcgen05.mma / tcgen05.commit issued by one lane that loops alone (the other 31 lanes of
+//     its warp parked at a barrier) costs that lane 45 to 270 cycles depending on how its
+//     operands are computed; issued from a converged warp under elect.sync with warp-uniform
+//     operands it costs ~23 (M = 128, N = 16, K = 16, A in TMEM);
+//   * a tcgen05.commit drains the tensor pipe (~75 cycles in which no MMA starts): with one
+//     commit per A slot and per consumer the pipe spent half its time drained, hence two
+//     commits per stage and barriers shared by every consumer of the same event;
+//   * every mbarrier wait costs its warp ~100 cycles even when the phase is already complete.
+// What bounds the kernel now is that TMEM holds only one stage of A next to the accumulators
+// (256 columns per CTA, two CTAs per SM): conversion of stage j + 1 cannot start before the MMAs
+// of stage j have read the slot, so conversion and MMA latencies add up instead of overlapping.
+//
+// TMEM columns (256 allocated, two CTAs per SM): D[2 buffers][3 tiles][16] = 96,
+// A[4 quarter-stage slots][2 tiles][2 steps][8] = 128, constant tile 8.  Lane l of quarter q holds
+// output column  64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8  of the slab.
 //
 // All mbarrier waits are bounded (tc_ptx.cuh); a wait that runs out aborts the CTA cleanly.
 #include <cooperative_groups.h>
 
-#include "stream_core.cuh"
+#include "common.cuh"
 #include "tc_ptx.cuh"
 
 namespace cg = cooperative_groups;
@@ -40,25 +58,27 @@ namespace {
 
 using namespace tc;
 
-constexpr int kCvThreads = 128;                 // conversion threads
-constexpr int kTsThreads = kCvThreads + 32;     // + control warp
-constexpr int kTsBN = 256, kTsBK = 128, kTsStages = 3;
+constexpr int kTsBN = 256, kTsBK = 128;
 constexpr int kNT = 16;                         // tokens padded to the MMA's N
+constexpr int kRing = 5;                        // stages in flight
 constexpr int kTsWBytes = kTsBK * (kTsBN / kPack) * 4;  // 16384
 constexpr int kTsXBytes = kNT * kTsBK * 2;              // 4096: two [16 x 64] tiles
-constexpr int kTsStageBytes = kTsWBytes + kTsXBytes;
-constexpr int kTsRingBytes = kTsStages * kTsStageBytes;  // 61440
-constexpr int kTsRedPitch = kTsBN + 8;                   // floats
-// padded so that at most two CTAs share an SM (each allocates 256 of the 512 TMEM columns)
-constexpr int kTsSmemBytes = 78 * 1024;
+constexpr int kTsStageBytes = kTsWBytes + kTsXBytes;    // 20480
+constexpr int kTsRingBytes = kRing * kTsStageBytes;     // 102400
+constexpr int kTsRedPitch = kTsBN + 8;                  // floats
+constexpr int kTsBarBytes = 256;
+constexpr int kTsSmemBytes = kTsRingBytes + kTsBarBytes + 1024;  // + alignment slack
+constexpr int kCvWarps = 8, kFoldWarps = 4;
+constexpr int kFoldWarp0 = kCvWarps, kIssueWarp = kCvWarps + kFoldWarps;
+constexpr int kProducerWarp = kIssueWarp + 1;
+constexpr int kTsThreads = 32 * (kProducerWarp + 1);  // 448
 constexpr int kTmemColsTs = 256;
 constexpr int kColD = 0;      // + buffer * 48 + tile * 16
-constexpr int kColA = 96;     // + half * 64 + tile * 32 + step * 8
+constexpr int kColA = 96;     // + slot * 32 + tile * 16 + step * 8
 constexpr int kColOnes = 224;
+static_assert(kNT * kTsRedPitch * 4 <= kTsRingBytes, "partial tile must fit the idle ring");
 
 struct TsParams {
-  const __half* x;
-  const uint32_t* qweight;
   const __half* scales;
   const uint32_t* qzeros;
   const __half* bias;
@@ -66,8 +86,10 @@ struct TsParams {
   int M, N, K;
 };
 
-__device__ __forceinline__ void cv_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kCvThreads) : "memory");
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ void tmem_st_16x256b(uint32_t taddr, uint32_t r0, uint32_t r1,
                                                 uint32_t r2, uint32_t r3) {
@@ -75,13 +97,11 @@ __device__ __forceinline__ void tmem_st_16x256b(uint32_t taddr, uint32_t r0, uin
                "r"(r0), "r"(r1), "r"(r2), "r"(r3)
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
+        "=r"(r[7])
       : "r"(taddr)
       : "memory");
 }
@@ -97,7 +117,9 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
 }
 
 template <bool EXACT>
-__global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p) {
+__global__ void __launch_bounds__(kTsThreads, 2)
+gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const TsParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int s_abort;
   __shared__ uint32_t s_tmem_base;
@@ -109,9 +131,12 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   float* red = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
   const uint32_t bar_base = smem_base + kTsRingBytes;
-  auto a_full = [&](int h) { return bar_base + 8 * h; };
-  auto a_empty = [&](int h) { return bar_base + 16 + 8 * h; };
-  auto d_empty = [&](int b) { return bar_base + 32 + 8 * b; };
+  auto raw_full = [&](int s) { return bar_base + 8 * s; };
+  auto raw_empty = [&](int s) { return bar_base + 8 * (kRing + s); };
+  auto a_full = [&](int c) { return bar_base + 8 * (2 * kRing + c); };
+  auto done0 = [&]() { return bar_base + 8 * (2 * kRing + 4); };
+  auto done1 = [&](int b) { return bar_base + 8 * (2 * kRing + 5 + b); };
+  auto d_empty = [&](int b) { return bar_base + 8 * (2 * kRing + 7 + b); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int words = p.N / kPack;
@@ -123,15 +148,21 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
 
   if (tid == 0) {
     s_abort = 0;
-    for (int h = 0; h < 2; ++h) {
-      mbar_init(a_full(h), kCvThreads);
-      mbar_init(a_empty(h), 1);
-      mbar_init(d_empty(h), kCvThreads);
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(raw_full(s), 1);
+      mbar_init(raw_empty(s), kCvWarps);
+    }
+    for (int c = 0; c < 4; ++c)
+      mbar_init(a_full(c), 4 * 32);  // the four warps (one per lane quarter) that fill slot c
+    mbar_init(done0(), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(done1(b), 1);
+      mbar_init(d_empty(b), kFoldWarps * 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
                  "r"((uint32_t)kTmemColsTs)
@@ -143,139 +174,185 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
 
-  float tot0[kNT], tot1[kNT];
-#pragma unroll
-  for (int m = 0; m < kNT; ++m) tot0[m] = tot1[m] = 0.f;
-
-  if (warp == 4) {
-    // ------------------------------------------------------------------ control: MMA issue
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ producer: TMA
     if (lane == 0) {
-      // D fp32, A/B fp16, both K-major, N = 16 tokens, M = 128 weight columns
-      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kNT >> 3) << 17) | (8u << 24);
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       bool ok = true;
       for (int j = 0; j < nst && ok; ++j) {
-        const uint32_t xt = smem_base + (j % kTsStages) * kTsStageBytes + kTsWBytes;
-        const int b = j & 1;
-        for (int h = 0; h < 2 && ok; ++h) {
-          ok = mbar_wait(a_full(h), (uint32_t)(j & 1), &s_abort, 11);
-          if (ok && h == 0 && j >= 2)
-            ok = mbar_wait(d_empty(b), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 12);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t dx = make_desc(xt + h * 2048, 16, 1024);
+        const int s = j % kRing;
+        if (j >= kRing) ok = mbar_wait(raw_empty(s), (uint32_t)((j / kRing - 1) & 1), &s_abort, 21);
+        if (!ok) break;
+        const uint32_t dst = smem_base + s * kTsStageBytes;
+        const int k0 = (st_begin + j) * kTsBK;
+        mbar_arrive_expect_tx(raw_full(s), kTsStageBytes);
+        tma_load_2d(dst, &map_w, word0, k0, raw_full(s));
+        tma_load_2d(dst + kTsWBytes, &map_x, k0, 0, raw_full(s));
+        tma_load_2d(dst + kTsWBytes + 2048, &map_x, k0 + 64, 0, raw_full(s));
+      }
+    }
+  } else if (warp == kIssueWarp) {
+    // ------------------------------------------------------------------ MMA issue
+    // The whole warp runs the loop and stays converged; one elected lane issues (see elect_one).
+    // Two commits per stage: done0 after the first half (A slots 0, 1 free again) and done1[b]
+    // at the end (A slots 2, 3 free, D[b] complete, x tile of the stage read).
+    // D fp32, A/B fp16, both K-major, N = 16 tokens, M = 128 weight columns
+    constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kNT >> 3) << 17) | (8u << 24);
+    // Operands of tcgen05 instructions live in uniform registers: keep everything they are
+    // computed from provably warp-uniform (broadcast bases, wrapping counters instead of
+    // divisions), otherwise every MMA pays for moving its operands across register files.
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t ring_u = __shfl_sync(0xffffffffu, smem_base, 0);
+    bool ok = true;
+    int s = 0;
+    uint32_t ring_phase = 0;
+    for (int j = 0; j < nst && ok; ++j) {
+      const int b = j & 1;
+      if (j >= 2) ok = mbar_wait(d_empty(b), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 11);
+      if (ok) ok = mbar_wait(raw_full(s), ring_phase, &s_abort, 12);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const uint32_t xt = ring_u + s * kTsStageBytes + kTsWBytes;
+      const uint32_t dcol = tmem_u + kColD + b * 48;
 #pragma unroll
-          for (int s4 = 0; s4 < 4; ++s4) {
-            const uint32_t acc = (h == 0 && s4 == 0) ? 0u : 1u;
-            const uint64_t db = dx + (uint64_t)((s4 * 32) >> 4);
-            const uint32_t dcol = tmem + kColD + b * 48;
-            const uint32_t acol = tmem + kColA + h * 64 + s4 * 8;
+      for (int c = 0; c < 4; ++c) {
+        // slot c converted (the constant tile was written before the first a_full[0])
+        ok = mbar_wait(a_full(c), (uint32_t)(j & 1), &s_abort, 13);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int step = 2 * c + e;
+            const uint64_t db = make_desc(xt + (step >> 2) * 2048, 16, 1024) +
+                                (uint64_t)(((step & 3) * 32) >> 4);
+            const uint32_t acc = step == 0 ? 0u : 1u;
+            const uint32_t acol = tmem_u + kColA + c * 32 + e * 8;
             umma_f16_ts(dcol, acol, db, idesc, acc);
-            umma_f16_ts(dcol + 16, acol + 32, db, idesc, acc);
-            if (!EXACT) umma_f16_ts(dcol + 32, tmem + kColOnes, db, idesc, acc);
+            umma_f16_ts(dcol + 16, acol + 16, db, idesc, acc);
+            if (!EXACT) umma_f16_ts(dcol + 32, tmem_u + kColOnes, db, idesc, acc);
           }
-          umma_commit(a_empty(h));
+          if (c == 1) umma_commit(done0());
+          if (c == 3) umma_commit(done1(b));
         }
+        __syncwarp();
+      }
+      if (++s == kRing) {
+        s = 0;
+        ring_phase ^= 1u;
+      }
+    }
+  } else if (warp >= kFoldWarp0) {
+    // ------------------------------------------------------------------ fold
+    const int q = warp - kFoldWarp0;  // == warp % 4: this warp's TMEM lane quarter
+    const uint32_t lane_q = (uint32_t)(q * 32) << 16;
+    // this thread's TMEM lane holds one output column per weight tile
+    const int hp = lane >> 4, odd = (lane >> 3) & 1, gp = lane & 7;
+    const int fold_word = min(word0 + 8 * q + gp, words - 1);
+    const int col0 = 2 * hp + odd, col1 = 2 * (2 + hp) + odd;  // column inside the word
+    const int nib0 = hp + 4 * odd, nib1 = (2 + hp) + 4 * odd;   // its nibble position
+    float tot0[kNT], tot1[kNT];
+#pragma unroll
+    for (int m = 0; m < kNT; ++m) tot0[m] = tot1[m] = 0.f;
+
+    const __half* sp = p.scales + (size_t)st_begin * p.N + fold_word * 8;
+    const uint32_t* zp = p.qzeros + (size_t)st_begin * words + fold_word;
+    __half s0n = __float2half(0.f), s1n = s0n;
+    uint32_t zwn = 0;
+    if (nst > 0) {
+      s0n = __ldg(sp + col0);
+      s1n = __ldg(sp + col1);
+      zwn = __ldg(zp);
+    }
+    bool ok = true;
+    for (int j = 0; j < nst && ok; ++j) {
+      const int b = j & 1;
+      const float s0 = __half2float(s0n), s1 = __half2float(s1n);
+      const uint32_t zw = zwn;
+      if (j + 1 < nst) {
+        s0n = __ldg(sp + (size_t)(j + 1) * p.N + col0);
+        s1n = __ldg(sp + (size_t)(j + 1) * p.N + col1);
+        zwn = __ldg(zp + (size_t)(j + 1) * words);
+      }
+      // odd half-quarters hold nibbles kept in place (16 q), so their zero point is 16 z
+      const float zf = hp ? 16.f : 1.f;
+      const float z0 = zf * (float)((zw >> (4 * nib0)) & 0xF);
+      const float z1 = zf * (float)((zw >> (4 * nib1)) & 0xF);
+      ok = mbar_wait(done1(b), (uint32_t)((j >> 1) & 1), &s_abort, 14);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t dcol = tmem + lane_q + kColD + b * 48;
+#pragma unroll
+      for (int th = 0; th < 2; ++th) {
+        uint32_t d0[8], d1[8], dx[8];
+        tmem_ld8(dcol + th * 8, d0);
+        tmem_ld8(dcol + 16 + th * 8, d1);
+        if (!EXACT) tmem_ld8(dcol + 32 + th * 8, dx);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (th == 1) {
+          tc_fence_before();
+          mbar_arrive(d_empty(b));
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          if (EXACT) {
+            tot0[th * 8 + m] = fmaf(s0, __uint_as_float(d0[m]), tot0[th * 8 + m]);
+            tot1[th * 8 + m] = fmaf(s1, __uint_as_float(d1[m]), tot1[th * 8 + m]);
+          } else {
+            const float xs = __uint_as_float(dx[m]);
+            tot0[th * 8 + m] = fmaf(s0, fmaf(-z0, xs, __uint_as_float(d0[m])), tot0[th * 8 + m]);
+            tot1[th * 8 + m] = fmaf(s1, fmaf(-z1, xs, __uint_as_float(d1[m])), tot1[th * 8 + m]);
+          }
+        }
+      }
+    }
+    // ---- partial tile to shared memory: red[token][column of the slab] (the ring is idle:
+    //      the last done1 implies every stage was converted and read by the tensor core) ----
+    if (ok) {
+      const float f = EXACT ? 1.f : (hp ? 1048576.f : 16777216.f);  // undo 2^-20 / 2^-24
+      const int nl0 = 64 * q + 8 * gp + col0, nl1 = 64 * q + 8 * gp + col1;
+#pragma unroll
+      for (int m = 0; m < kNT; ++m) {
+        red[m * kTsRedPitch + nl0] = tot0[m] * f;
+        red[m * kTsRedPitch + nl1] = tot1[m] * f;
       }
     }
   } else {
     // ------------------------------------------------------------------ conversion warps
     const int g = lane >> 2, t = lane & 3;
-    const int q = warp;  // TMEM lane quarter
-    // producer mapping (as in stream_core.cuh)
-    const int wc = word0 + (tid & 7) * 4;
-    const bool wvalid = wc < words;
-    const uint32_t* wsrc = p.qweight + (wvalid ? wc : 0);
-    const int pr_row = tid >> 3;
-    const uint32_t pr_sw = (uint32_t)(((tid & 7) ^ (int)stream::row_swizzle(pr_row)) << 4);
-    // x tile: rows (tid >> 4) and + 8, 16-byte chunk tid & 15 of the stage's 128 columns
-    const int xr = tid >> 4, xch = tid & 15;
-    const uint32_t x_dst = (uint32_t)((xch >> 3) * 2048 + xr * 128 + (((xch & 7) ^ (xr & 7)) << 4));
-    const bool xv0 = xr < p.M, xv1 = xr + 8 < p.M;
-    const __half* xs0 = p.x + (size_t)(xv0 ? xr : 0) * p.K + xch * 8;
-    const __half* xs1 = p.x + (size_t)(xv1 ? xr + 8 : 0) * p.K + xch * 8;
-
-    auto issue_stage = [&](int st, int buf) {
-      const uint32_t wbase = smem_base + buf * kTsStageBytes;
-      const int k0 = st * kTsBK;
-      const uint32_t* s0 = wsrc + (size_t)k0 * words;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = pr_row + 16 * i;
-        cp_async16(wbase + row * 128 + pr_sw, s0 + (size_t)row * words, wvalid);
-      }
-      const uint32_t xbase = wbase + kTsWBytes + x_dst;
-      cp_async16(xbase, xs0 + k0, xv0);
-      cp_async16(xbase + 8 * 128, xs1 + k0, xv1);
-    };
-
-    // fragment-read mapping
-    const int chunk_id = 2 * q + (g >> 2);
-    const uint32_t offA = ((chunk_id ^ (2 * t)) << 4) + (g & 3) * 4;
-    const uint32_t offB = ((chunk_id ^ (2 * t + 1)) << 4) + (g & 3) * 4;
+    const int q = warp & 3, par = warp >> 2;
     const uint32_t lane_q = (uint32_t)(q * 32) << 16;
-    // fold mapping: this thread's TMEM lane holds one output column per weight tile
-    const int hp = lane >> 4, odd = (lane >> 3) & 1, gp = lane & 7;
-    const int fold_word = min(word0 + 8 * q + gp, words - 1);
-    const int col0 = 2 * hp + odd, col1 = 2 * (2 + hp) + odd;  // column inside the word
-    const int nib0 = hp + 4 * odd, nib1 = (2 + hp) + 4 * odd;   // its nibble position
+    // raw tile as TMA leaves it: row r at r * 128, 16-byte chunk c at position c ^ (r % 8).
+    // This lane reads word 8 q + g of rows 16 s + 4 t + rr.
+    const int chunk_id = 2 * q + (g >> 2);
+    uint32_t off[4];
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      const int r = 4 * t + rr;
+      off[rr] = (uint32_t)(r * 128 + ((chunk_id ^ (r & 7)) << 4) + (g & 3) * 4);
+    }
     const int conv_word = min(word0 + 8 * q + g, words - 1);
 
-    if (!EXACT) {
+    if (!EXACT && par == 0) {
       // constant A tile: every k slot of every lane = 2^-24 (fp16 subnormal 0x0001)
       tmem_st_16x256b(tmem + lane_q + kColOnes, 0x00010001u, 0x00010001u, 0x00010001u, 0x00010001u);
       tmem_st_16x256b(tmem + lane_q + (16u << 16) + kColOnes, 0x00010001u, 0x00010001u,
                       0x00010001u, 0x00010001u);
     }
-
-    issue_stage(st_begin, 0);
-    cp_async_commit();
-    if (nst > 1) issue_stage(st_begin + 1, 1);
-    cp_async_commit();
+    uint32_t zw_n = 0;
+    if (EXACT && nst > 0) zw_n = __ldg(p.qzeros + (size_t)st_begin * words + conv_word);
 
     bool ok = true;
-    auto fold = [&](int jj) {
-      // accumulators of local stage jj are complete (a_empty[1] of that stage was observed)
-      const int b = jj & 1;
-      const int grp = st_begin + jj;
-      const __half s0h = __ldg(p.scales + (size_t)grp * p.N + fold_word * 8 + col0);
-      const __half s1h = __ldg(p.scales + (size_t)grp * p.N + fold_word * 8 + col1);
-      const uint32_t zw = __ldg(p.qzeros + (size_t)grp * words + fold_word);
-      tc_fence_after();
-      uint32_t d0[16], d1[16], dx[16];
-      const uint32_t dcol = tmem + lane_q + kColD + b * 48;
-      tmem_ld16(dcol, d0);
-      tmem_ld16(dcol + 16, d1);
-      if (!EXACT) tmem_ld16(dcol + 32, dx);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      tc_fence_before();
-      mbar_arrive(d_empty(b));
-      const float s0 = __half2float(s0h), s1 = __half2float(s1h);
-      if (EXACT) {
-#pragma unroll
-        for (int m = 0; m < kNT; ++m) {
-          tot0[m] = fmaf(s0, __uint_as_float(d0[m]), tot0[m]);
-          tot1[m] = fmaf(s1, __uint_as_float(d1[m]), tot1[m]);
-        }
-      } else {
-        // odd half-quarters hold nibbles kept in place (16 q), so their zero point is 16 z
-        const float zf = hp ? 16.f : 1.f;
-        const float z0 = zf * (float)((zw >> (4 * nib0)) & 0xF);
-        const float z1 = zf * (float)((zw >> (4 * nib1)) & 0xF);
-#pragma unroll
-        for (int m = 0; m < kNT; ++m) {
-          const float xs = __uint_as_float(dx[m]);
-          tot0[m] = fmaf(s0, fmaf(-z0, xs, __uint_as_float(d0[m])), tot0[m]);
-          tot1[m] = fmaf(s1, fmaf(-z1, xs, __uint_as_float(d1[m])), tot1[m]);
-        }
-      }
-    };
-
     for (int j = 0; j < nst && ok; ++j) {
-      const uint32_t wsm = smem_base + (j % kTsStages) * kTsStageBytes;
+      const int s = j % kRing;
+      const uint32_t wsm = smem_base + s * kTsStageBytes;
       // EXACT: zero registers of this thread's packed word for the group (= stage)
       __half2 zu[4], zv[4];
       if (EXACT) {
-        const uint32_t zw = __ldg(p.qzeros + (size_t)(st_begin + j) * words + conv_word);
+        const uint32_t zw = zw_n;
+        if (j + 1 < nst) zw_n = __ldg(p.qzeros + (size_t)(st_begin + j + 1) * words + conv_word);
         const uint32_t uz = prmt(zw, zw, 0x1010), vz = prmt(zw, zw, 0x3232);
         const __half2 m16 = __float2half2_rn(-0.0625f);
         zu[0] = as_half2(lop3_and_or(uz, 0x000F000Fu, 0x64006400u));
@@ -287,26 +364,32 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
         zu[3] = __hmul2(as_half2(lop3_and_or(uz >> 8, 0x00F000F0u, 0x64006400u)), m16);
         zv[3] = __hmul2(as_half2(lop3_and_or(vz >> 8, 0x00F000F0u, 0x64006400u)), m16);
       }
-      cp_async_wait<1>();
-      cv_sync();
-
-      for (int h = 0; h < 2 && ok; ++h) {
-        if (j >= 1) ok = mbar_wait(a_empty(h), (uint32_t)((j - 1) & 1), &s_abort, 13 + h);
-        if (!ok) break;
-        if (h == 1) {
-          // stage j-1 is fully consumed by the tensor core: refill its ring slot, fold it
-          if (j + 2 < nst) issue_stage(st_begin + j + 2, (j + 2) % kTsStages);
-          cp_async_commit();
-          if (j >= 1) fold(j - 1);
-        }
+      ok = mbar_wait(raw_full(s), (uint32_t)((j / kRing) & 1), &s_abort, 15);
+      if (!ok) break;
 #pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) {
-          const int s = 4 * h + s4;
-          const uint32_t rowA = wsm + (16 * s + 4 * t) * 128;
-          const uint32_t w0 = stream::lds32(rowA + offA);
-          const uint32_t w1 = stream::lds32(rowA + 128 + offB);
-          const uint32_t w2 = stream::lds32(rowA + 2 * 128 + offA);
-          const uint32_t w3 = stream::lds32(rowA + 3 * 128 + offB);
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = par + 2 * cc;  // quarter-stage = A slot
+        // slot c of the previous stage must have been read by the tensor core
+        if (j >= 1) {
+          if (cc == 0) {
+            ok = mbar_wait(done0(), (uint32_t)((j - 1) & 1), &s_abort, 16);
+          } else {
+            ok = mbar_wait(done1((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), &s_abort, 17);
+            // the previous stage is finished with: this warp's reads of its packed weights were
+            // consumed by the conversion, the tensor core has read its x tile
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(raw_empty((j - 1) % kRing));
+          }
+        }
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t rowA = wsm + (16 * (2 * c + e)) * 128;
+          const uint32_t w0 = lds32(rowA + off[0]);
+          const uint32_t w1 = lds32(rowA + off[1]);
+          const uint32_t w2 = lds32(rowA + off[2]);
+          const uint32_t w3 = lds32(rowA + off[3]);
           const uint32_t u0 = prmt(w0, w1, 0x5410), v0 = prmt(w0, w1, 0x7632);
           const uint32_t u1 = prmt(w2, w3, 0x5410), v1 = prmt(w2, w3, 0x7632);
           const uint32_t u0h = u0 >> 8, v0h = v0 >> 8, u1h = u1 >> 8, v1h = v1 >> 8;
@@ -340,35 +423,20 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
               r3 = sv1 & mask;
             }
             // half-quarter i & 1 of this warp's lanes, weight tile i >> 1
-            tmem_st_16x256b(tmem + lane_q + ((uint32_t)((i & 1) * 16) << 16) + kColA + h * 64 +
-                                (i >> 1) * 32 + s4 * 8,
+            tmem_st_16x256b(tmem + lane_q + ((uint32_t)((i & 1) * 16) << 16) + kColA + c * 32 +
+                                (i >> 1) * 16 + e * 8,
                             r0, r1, r2, r3);
           }
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        if (h == 0) fence_proxy_async();  // this thread's x-tile bytes -> tensor core's proxy
         tc_fence_before();
-        mbar_arrive(a_full(h));
+        mbar_arrive(a_full(c));
       }
-    }
-    if (ok && nst > 0) {
-      ok = mbar_wait(a_empty(1), (uint32_t)((nst - 1) & 1), &s_abort, 15);
-      if (ok) fold(nst - 1);
-    }
-    cp_async_wait<0>();
-    cv_sync();  // ring idle: reuse it for the partial tile
-
-    // ---- partial tile to shared memory: red[token][column of the slab] ----
-    const float f = EXACT ? 1.f : (hp ? 1048576.f : 16777216.f);  // undo 2^-20 / 2^-24
-    const int nl0 = 64 * q + 8 * gp + col0, nl1 = 64 * q + 8 * gp + col1;
-#pragma unroll
-    for (int m = 0; m < kNT; ++m) {
-      red[m * kTsRedPitch + nl0] = tot0[m] * f;
-      red[m * kTsRedPitch + nl1] = tot1[m] * f;
     }
   }
 
   // ---- reduction over the cluster ranks through distributed shared memory ----
+  __syncthreads();
   cluster.sync();
   if (!s_abort) {
     constexpr int kUnits = kTsBN / 8;
@@ -406,7 +474,7 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
                  "r"((uint32_t)kTmemColsTs)
@@ -415,7 +483,8 @@ __global__ void __launch_bounds__(kTsThreads, 2) gemm_ts_kernel(const TsParams p
 }
 
 template <bool EXACT>
-int launch_ts(const TsParams& p, cudaStream_t stream) {
+int launch_ts(const CUtensorMap& map_w, const CUtensorMap& map_x, const TsParams& p,
+              cudaStream_t stream) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -429,9 +498,19 @@ int launch_ts(const TsParams& p, cudaStream_t stream) {
   }
   const int slabs = (p.N + kTsBN - 1) / kTsBN;
   const int KT = p.K / kTsBK;
-  int S = (2 * sm_count()) / slabs;
-  S = S < 1 ? 1 : (S > 8 ? 8 : S);
-  while (S > 1 && KT / S < 2) --S;
+  // cluster size (K split): the one that needs the least time in units of a whole-K CTA,
+  // rounds of 2 CTAs per SM times 1 / S; ties go to the smaller cluster
+  const int slots = 2 * sm_count();
+  int S = 1;
+  double best = 1e30;
+  for (int s = 1; s <= 8 && KT / s >= 4; ++s) {
+    const int rounds = (slabs * s + slots - 1) / slots;
+    const double cost = (double)rounds / s + 0.02 * s;
+    if (cost < best) {
+      best = cost;
+      S = s;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S, slabs, 1);
   cfg.blockDim = dim3(kTsThreads, 1, 1);
@@ -444,7 +523,7 @@ int launch_ts(const TsParams& p, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, p) != cudaSuccess) {
     cudaGetLastError();
     return AWQ_B200_ERR_LAUNCH;
   }
@@ -454,6 +533,7 @@ int launch_ts(const TsParams& p, cudaStream_t stream) {
 }  // namespace
 
 bool gemm_ts_supported(int M, int N, int K, int group) {
+  // N % 32: 16-byte TMA row pitch of the packed weights; K % 128: whole stages
   return M >= 1 && M <= kNT && N % 32 == 0 && K % kTsBK == 0 && group == 128;
 }
 
@@ -461,8 +541,18 @@ int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scale
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, bool exact, cudaStream_t stream) {
   if (!gemm_ts_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
-  TsParams p{x, qweight, scales, qzeros, bias, out, M, N, K};
-  return exact ? launch_ts<true>(p, stream) : launch_ts<false>(p, stream);
+  CUtensorMap map_w, map_x;
+  // packed weights [K rows][N / 8 words], box [128 rows x 32 words], 128-byte swizzle
+  if (int rc = encode_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, (uint64_t)(N / kPack),
+                             (uint64_t)K, (uint64_t)(N / kPack) * 4, kTsBN / kPack, kTsBK,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  // activations [M rows][K], box [16 tokens x 64 k] (rows past M read as zero), 128-byte swizzle
+  if (int rc = encode_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)K, (uint64_t)M,
+                             (uint64_t)K * 2, 64, kNT, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  TsParams p{scales, qzeros, bias, out, M, N, K};
+  return exact ? launch_ts<true>(map_w, map_x, p, stream) : launch_ts<false>(map_w, map_x, p, stream);
 }
 
 int ts_device_status(int* out) {

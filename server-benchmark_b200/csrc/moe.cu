@@ -3,10 +3,10 @@
 //   topk_softmax_kernel   one warp per token: softmax over E logits, k rounds of warp arg-max
 //                         (ties -> lower expert id), optional renormalisation.
 //   moe_align_kernel      stable counting sort of the T*k (token, slot) pairs by expert with
-//                         every expert's run padded to the GEMM row block; one CTA per 8 experts,
-//                         each CTA rebuilds the (cheap) histogram and prefix itself so a single
-//                         launch suffices; within an expert a warp ranks pairs with ballots, in
-//                         ascending flat index, hence a deterministic order.
+//                         every expert's run padded to the GEMM row block; one CTA per 256 pairs,
+//                         each CTA rebuilds the (cheap) histograms itself so a single launch
+//                         suffices; ranks come from warp match masks, in ascending flat index,
+//                         hence a deterministic order.
 //   moe_gemm1_kernel      per (row block, 128 gate + 128 up columns): x rows gathered through the
 //                         permutation, expert weights streamed (stream_core.cuh), epilogue
 //                         silu(gate) * up -> fp16 activation in permuted row order.
@@ -116,58 +116,97 @@ topk_softmax_kernel(const T* __restrict__ gating, int tokens, int E, int topk, i
 
 // ------------------------------------------------------------------------------- permutation
 
-constexpr int kAlignThreads = 256;
-constexpr int kAlignExpertsPerCta = kAlignThreads / 32;
-constexpr int kMaxExperts = 1024;
+constexpr int kAlignThreads = 256;                 // 8 warps
+constexpr int kAlignChunk = kAlignThreads;         // ids ranked by one CTA
+constexpr int kAlignMaxCtas = 296;                 // bounds the redundant histogram passes
 
+// One CTA ranks a contiguous range of flat ids, 256 at a time.  Every CTA first builds, in shared memory,
+// the histogram of ALL ids (-> padded expert offsets) and the histogram of the ids that precede
+// its range (-> where its own entries start inside each expert's run); that redundant pass over
+// the id list costs a few microseconds and saves a second launch or a grid-wide barrier.  Inside
+// the chunk the order is kept by ranking with warp match masks plus per-warp counts, so the
+// result is the stable counting sort the oracle defines, independent of scheduling.
 __global__ void __launch_bounds__(kAlignThreads)
 moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
                  const int32_t* __restrict__ expert_map, int32_t* __restrict__ sorted_ids,
                  int64_t capacity, int32_t* __restrict__ expert_ids,
                  int32_t* __restrict__ num_post_pad) {
-  __shared__ int hist[kMaxExperts];
-  __shared__ int offs[kMaxExperts + 1];
+  extern __shared__ int sm[];
+  int* total = sm;                 // [E]   histogram of all ids
+  int* prior = sm + E;             // [E]   histogram of ids before this chunk
+  int* offs = sm + 2 * E;          // [E+1] padded exclusive prefix
+  int* wcnt = sm + 3 * E + 1;      // [8][E] per-warp histogram of this chunk
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int e = tid; e < E; e += kAlignThreads) hist[e] = 0;
+  // contiguous range of chunks owned by this CTA
+  const int nchunks = (numel + kAlignChunk - 1) / kAlignChunk;
+  const int per_cta = (nchunks + gridDim.x - 1) / gridDim.x;
+  const int first = blockIdx.x * per_cta * kAlignChunk;
+  const int last = min(numel, first + per_cta * kAlignChunk);
+  for (int i = tid; i < 3 * E + 1 + 8 * E; i += kAlignThreads) sm[i] = 0;
   __syncthreads();
+  auto valid = [&](int id) {
+    return id >= 0 && id < E && (expert_map == nullptr || expert_map[id] >= 0);
+  };
+#pragma unroll 4
   for (int i = tid; i < numel; i += kAlignThreads) {
     const int id = ids[i];
-    if (id >= 0 && id < E && (expert_map == nullptr || expert_map[id] >= 0))
-      atomicAdd(&hist[id], 1);
+    if (valid(id)) {
+      atomicAdd(&total[id], 1);
+      if (i < first) atomicAdd(&prior[id], 1);
+    }
   }
   __syncthreads();
   if (tid == 0) {
     int run = 0;
     for (int e = 0; e < E; ++e) {
       offs[e] = run;
-      run += ((hist[e] + block - 1) / block) * block;
+      run += ((total[e] + block - 1) / block) * block;
     }
     offs[E] = run;
   }
   __syncthreads();
-  const int total = offs[E];
-
-  const int e = blockIdx.x * kAlignExpertsPerCta + warp;
-  if (e < E && hist[e] > 0) {
-    const int base = offs[e];
-    const int padded = offs[e + 1] - base;
-    int cnt = 0;
-    for (int i0 = 0; i0 < numel; i0 += 32) {
-      const int i = i0 + lane;
-      const bool m = i < numel && ids[i] == e;
-      const unsigned b = __ballot_sync(0xffffffffu, m);
-      if (m) sorted_ids[base + cnt + __popc(b & ((1u << lane) - 1u))] = i;
-      cnt += __popc(b);
+  const int post = offs[E];
+  for (int chunk0 = first; chunk0 < last; chunk0 += kAlignChunk) {
+    // this thread's id and its rank among equal ids of its warp
+    const int idx = chunk0 + tid;
+    const int my = idx < last ? ids[idx] : -1;
+    const bool mine = idx < last && valid(my);
+    const unsigned peers = __match_any_sync(0xffffffffu, mine ? my : -1 - lane);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (mine && rank_in_warp == 0) wcnt[warp * E + my] = __popc(peers);
+    __syncthreads();
+    if (mine) {
+      int before = prior[my];
+      for (int w = 0; w < warp; ++w) before += wcnt[w * E + my];
+      sorted_ids[offs[my] + before + rank_in_warp] = idx;
     }
-    for (int j = cnt + lane; j < padded; j += 32) sorted_ids[base + j] = numel;
-    const int local = expert_map == nullptr ? e : expert_map[e];
-    for (int bk = lane; bk < padded / block; bk += 32) expert_ids[base / block + bk] = local;
+    __syncthreads();
+    if (chunk0 + kAlignChunk < last) {  // fold this chunk into the running counts
+      for (int e = tid; e < E; e += kAlignThreads) {
+        int c = 0;
+        for (int w = 0; w < kAlignThreads / 32; ++w) {
+          c += wcnt[w * E + e];
+          wcnt[w * E + e] = 0;
+        }
+        prior[e] += c;
+      }
+      __syncthreads();
+    }
   }
+  // padding entries, block -> expert table and the tail are written by the first CTA
   if (blockIdx.x == 0) {
-    if (tid == 0) num_post_pad[0] = total;
-    for (int64_t j = total + tid; j < capacity; j += kAlignThreads) sorted_ids[j] = numel;
+    for (int e = warp; e < E; e += kAlignThreads / 32) {
+      const int cnt = total[e];
+      if (cnt == 0) continue;
+      const int base = offs[e], padded = offs[e + 1] - base;
+      for (int j = cnt + lane; j < padded; j += 32) sorted_ids[base + j] = numel;
+      const int local = expert_map == nullptr ? e : expert_map[e];
+      for (int bk = lane; bk < padded / block; bk += 32) expert_ids[base / block + bk] = local;
+    }
+    if (tid == 0) num_post_pad[0] = post;
+    for (int64_t j = post + tid; j < capacity; j += kAlignThreads) sorted_ids[j] = numel;
     const int64_t nblk = (capacity + block - 1) / block;
-    for (int64_t bk = total / block + tid; bk < nblk; bk += kAlignThreads) expert_ids[bk] = -1;
+    for (int64_t bk = post / block + tid; bk < nblk; bk += kAlignThreads) expert_ids[bk] = -1;
   }
 }
 
@@ -447,8 +486,10 @@ int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int 
 int launch_moe_align(const int32_t* topk_ids, int numel, int E, int block,
                      const int32_t* expert_map, int32_t* sorted_ids, int64_t sorted_capacity,
                      int32_t* expert_ids, int32_t* num_post_pad, cudaStream_t stream) {
-  const int grid = (E + kAlignExpertsPerCta - 1) / kAlignExpertsPerCta;
-  moe_align_kernel<<<grid, kAlignThreads, 0, stream>>>(topk_ids, numel, E, block, expert_map,
+  const int nchunks = (numel + kAlignChunk - 1) / kAlignChunk;
+  const int grid = nchunks < 1 ? 1 : (nchunks < kAlignMaxCtas ? nchunks : kAlignMaxCtas);
+  const size_t smem = (size_t)(3 * E + 1 + 8 * E) * sizeof(int);  // <= 45 KB for E <= 1024
+  moe_align_kernel<<<grid, kAlignThreads, smem, stream>>>(topk_ids, numel, E, block, expert_map,
                                                        sorted_ids, sorted_capacity, expert_ids,
                                                        num_post_pad);
   return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
