@@ -46,7 +46,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel, as a ratio to
 # the launch's algorithmic bytes, from the ncu capture summarised in
 # profiles/gemm_stream_M16_K8192_N29568.md (capture of a smaller case, scaled by bytes)
-NCU_TRAFFIC_RATIO = 1.037
+NCU_TRAFFIC_RATIO = 1.051
 
 
 def shapes():
@@ -489,7 +489,7 @@ def run_case(args):
     """`--case kernel:M:K:N` launches one AWQ linear of that shape `--steps` times after
     `--warmup` launches and prints its CUDA-event time: the small, bounded command the ncu
     captures under profiles/ are taken with.  kernel: auto | stream | stream_exact | tcgen05 |
-    generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
+    ts | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
     import torch
 
     import build as awq_build
@@ -519,7 +519,8 @@ def run_case(args):
         else:
             kern = {"auto": awq_b200.KERNEL_AUTO, "stream": awq_b200.KERNEL_STREAM,
                     "stream_exact": awq_b200.KERNEL_STREAM_EXACT,
-                    "tcgen05": awq_b200.KERNEL_TCGEN05, "generic": awq_b200.KERNEL_GENERIC}[f[0]]
+                    "tcgen05": awq_b200.KERNEL_TCGEN05, "ts": awq_b200.KERNEL_TS,
+                    "generic": awq_b200.KERNEL_GENERIC}[f[0]]
             fn = lambda: awq_b200.awq_gemm(x, qw, s, qz, 8, kernel=kern)  # noqa: E731
         work = f"{f[0]} M={m} K={k} N={n}"
     for _ in range(args.warmup):
