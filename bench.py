@@ -15,7 +15,8 @@ value   device-resident: the step is captured once in a CUDA graph and replayed;
         CUDA events on the launching stream between barriers, max over ranks.
 e2e     the same step through the layer API (AWQLinearMethod.apply) with the activations in
         pinned host memory: host->device copy, four kernels, device->host copy of the outputs,
-        every step; weights stay resident in HBM as they do while serving.
+        every step; weights stay resident in HBM as they do while serving.  Three steps are in
+        flight on three streams (copies of one step overlap kernels of another).
 N > 1   replicas (the TP=1 scaling mode of the harness): every rank runs the same step on its
         own GPU, value is the sum; reported as weak scaling.  The tensor-parallel variant
         (column/row shards + NCCL all-reduce of the row-parallel outputs) is timed as well and
@@ -47,6 +48,7 @@ FALLBACK_HBM_GBS = 6650.0
 # the launch's algorithmic bytes, from the ncu capture summarised in
 # profiles/gemm_stream_M16_K8192_N29568.md (capture of a smaller case, scaled by bytes)
 NCU_TRAFFIC_RATIO = 1.051
+E2E_DEPTH = 3  # steps in flight in the end-to-end leg
 
 
 def shapes():
@@ -270,22 +272,47 @@ def run_cuda(args):
         ms = e0.elapsed_time(e1)
 
         # ---- e2e through the layer API with host buffers ----
-        def step_e2e():
-            for layer, xp, yp in zip(layers, x_pin, y_pin):
-                xd = xp.to(dev, non_blocking=True)
-                y = method.apply(layer, xd)
-                yp.copy_(y, non_blocking=True)
-            stream.synchronize()
+        # E2E_DEPTH steps are in flight, each on its own stream with its own pinned result
+        # buffers (a serving loop with that many requests in flight): the copies of one step
+        # overlap the kernels of another.  Every step still copies its inputs from pinned host
+        # memory and its four outputs back, and the host waits for a step's outputs before
+        # the buffers are used again.
+        side = [torch.cuda.Stream(device=dev) for _ in range(E2E_DEPTH)]
+        y_pins = [y_pin] + [[torch.empty_like(y).pin_memory() for y in y_pin]
+                            for _ in range(E2E_DEPTH - 1)]
+        landed = [None] * E2E_DEPTH
+
+        def step_e2e(i):
+            j = i % E2E_DEPTH
+            if landed[j] is not None:
+                landed[j].synchronize()  # outputs of the step that last used these buffers
+            with torch.cuda.stream(side[j]):
+                for layer, xp, yp in zip(layers, x_pin, y_pins[j]):
+                    xd = xp.to(dev, non_blocking=True)
+                    y = method.apply(layer, xd)
+                    yp.copy_(y, non_blocking=True)
+                landed[j] = torch.cuda.Event()
+                landed[j].record(side[j])
+
+        def drain():
+            for j in range(E2E_DEPTH):
+                if landed[j] is not None:
+                    landed[j].synchronize()
+                stream.wait_stream(side[j])
 
         e2e_steps = max(1, min(args.steps, 300))
-        for _ in range(3):
-            step_e2e()
+        for i in range(3 * E2E_DEPTH):
+            step_e2e(i)
+        drain()
         barrier()
         f0 = torch.cuda.Event(enable_timing=True)
         f1 = torch.cuda.Event(enable_timing=True)
         f0.record(stream)
-        for _ in range(e2e_steps):
-            step_e2e()
+        for j in range(E2E_DEPTH):
+            side[j].wait_stream(stream)
+        for i in range(e2e_steps):
+            step_e2e(i)
+        drain()
         f1.record(stream)
         barrier()
         ms_e2e = f0.elapsed_time(f1)
@@ -340,7 +367,7 @@ def run_cuda(args):
             "e2e": {"value": world * wbytes / sec_e2e / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": sum(m * k * 2 for _, (k, n) in shapes()),
                     "d2h_bytes_per_step": sum(m * n * 2 for _, (k, n) in shapes()),
-                    "steps": e2e_steps, "ms_per_step": sec_e2e * 1e3},
+                    "steps": e2e_steps, "ms_per_step": sec_e2e * 1e3, "steps_in_flight": E2E_DEPTH},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": sampler.summary(t_wall0, t_wall1),
         }
