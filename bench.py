@@ -516,7 +516,7 @@ def run_case(args):
     """`--case kernel:M:K:N` launches one AWQ linear of that shape `--steps` times after
     `--warmup` launches and prints its CUDA-event time: the small, bounded command the ncu
     captures under profiles/ are taken with.  kernel: auto | stream | stream_exact | tcgen05 |
-    ts | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
+    ts | wt | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
     import torch
 
     import build as awq_build
@@ -546,7 +546,7 @@ def run_case(args):
         else:
             kern = {"auto": awq_b200.KERNEL_AUTO, "stream": awq_b200.KERNEL_STREAM,
                     "stream_exact": awq_b200.KERNEL_STREAM_EXACT,
-                    "tcgen05": awq_b200.KERNEL_TCGEN05, "ts": awq_b200.KERNEL_TS,
+                    "tcgen05": awq_b200.KERNEL_TCGEN05, "ts": awq_b200.KERNEL_TS, "wt": awq_b200.KERNEL_WT,
                     "generic": awq_b200.KERNEL_GENERIC}[f[0]]
             fn = lambda: awq_b200.awq_gemm(x, qw, s, qz, 8, kernel=kern)  # noqa: E731
         work = f"{f[0]} M={m} K={k} N={n}"

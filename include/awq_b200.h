@@ -76,6 +76,7 @@ int awq_b200_dequantize(const void* qweight, const void* scales, const void* qze
 #define AWQ_B200_KERNEL_STREAM_EXACT 4 /* small-M kernel with the magic-number conversion */
 #define AWQ_B200_KERNEL_TS 5       /* M <= 16: registers -> TMEM weights, tcgen05.mma (A in TMEM) */
 #define AWQ_B200_KERNEL_TS_EXACT 6 /* the same with the magic-number conversion */
+#define AWQ_B200_KERNEL_WT 7       /* any M: dequantised weights registers -> TMEM (A operand), x via TMA as B */
 
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel);
 

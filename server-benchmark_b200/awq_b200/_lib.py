@@ -21,6 +21,7 @@ KERNEL_TCGEN05 = 3
 KERNEL_STREAM_EXACT = 4
 KERNEL_TS = 5
 KERNEL_TS_EXACT = 6
+KERNEL_WT = 7
 
 # name -> (restype, argtypes); kept in step with include/awq_b200.h
 PROTOTYPES = {

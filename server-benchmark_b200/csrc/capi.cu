@@ -112,6 +112,9 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
       if (!awq::gemm_ts_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
       return awq::launch_gemm_ts(xh, qw, sc, qz, bh, oh, M, N, K, group,
                                  kernel == AWQ_B200_KERNEL_TS_EXACT, st);
+    case AWQ_B200_KERNEL_WT:
+      if (!awq::gemm_wt_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+      return awq::launch_gemm_wt(xh, qw, sc, qz, bh, oh, M, N, K, group, st);
     case AWQ_B200_KERNEL_TCGEN05: {
       if (!awq::gemm_tc_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
       const size_t need = awq::gemm_tc_workspace_bytes(M, N, K, group);
@@ -130,10 +133,11 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
 int awq_b200_device_status(int* status) {
   if (!status) return AWQ_B200_ERR_NULL;
   if (int rc = check_device()) return rc;
-  int a = 0, b = 0;
+  int a = 0, b = 0, c = 0;
   if (int rc = awq::tc_device_status(&a)) return rc;
   if (int rc = awq::ts_device_status(&b)) return rc;
-  *status = a != 0 ? a : b;
+  if (int rc = awq::wt_device_status(&c)) return rc;
+  *status = a != 0 ? a : (b != 0 ? b : c);
   return AWQ_B200_OK;
 }
 

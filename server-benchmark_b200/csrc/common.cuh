@@ -127,6 +127,13 @@ int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scale
                    int group, bool exact, cudaStream_t stream);
 int ts_device_status(int* out);
 
+// gemm_wt.cu: dequantised weights in tensor memory as the A operand, activations as B
+bool gemm_wt_supported(int M, int N, int K, int group);
+int launch_gemm_wt(const __half* x, const uint32_t* qweight, const __half* scales,
+                   const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
+                   int group, cudaStream_t stream);
+int wt_device_status(int* out);
+
 int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                         int renormalize, float* topk_weights, int32_t* topk_ids,
                         int32_t* token_expert_indices, cudaStream_t stream);

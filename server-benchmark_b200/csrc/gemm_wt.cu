@@ -1,0 +1,517 @@
+// AWQ GEMM with the dequantised weights in tensor memory (any M; built for 32 < M <= 4096).
+//
+//   D[n, m] = sum_k W[k, n] * x[m, k]          (the transposed product)
+//
+// The weights are the A operand of tcgen05.mma.kind::f16 (M = 128 weight columns x K = 16) and
+// live in TMEM: conversion warps read the packed words from shared memory, dequantise them in
+// registers to (q - z) * s in fp16 and write the fragments with tcgen05.st.16x256b.  The
+// activations are the B operand ([NT tokens x 64 k] K-major, 128-byte swizzle) exactly as TMA
+// delivers them.  Compared with dequantising into a shared-memory B tile (gemm_tc.cu) the fp16
+// weights never cross shared memory: per 128-row stage of a 256-column slab the CTA moves
+// 48 + 16 KB (TMA writes, packed reads) + 2 * NT * 256 B (operand reads) instead of 352 KB,
+// which is what bounds the other kernel.
+//
+// One CTA per SM (all 512 TMEM columns): slab of 256 output columns = two interleaved A tiles
+// (tile u = columns 4u..4u+3 of every packed word), NT = 64 or 128 tokens, K range split over a
+// thread-block cluster when the grid would not fill the GPU.  Roles, joined by mbarrier rings:
+//
+//   producer (1 thread)    TMA: packed weights [128 rows x 128 B] + x [NT x 128 k] of a stage
+//                          into a 4-deep ring                                raw_full / raw_empty
+//   conversion (16 warps)  warp (q, r): TMEM lane quarter q, quarter-stage r (16-row steps 2r,
+//                          2r + 1) of every stage -> A slot (stage parity, r); the A ring holds
+//                          two stages, so conversion runs up to two stages ahead of the MMAs
+//                                                                            a_full / a_empty
+//   issue (1 warp)         converged warp, elected lane: per step one MMA per tile into
+//                          D[tile] (fp32, accumulated over the CTA's whole K range);
+//                          one tcgen05.commit per stage and ring             d_full
+//   epilogue               the conversion warps: tcgen05.ld -> fp32 partial tile in shared
+//                          memory -> sum over the cluster ranks through DSMEM -> fp16 (+ bias)
+//
+// TMEM columns: D[2 tiles][NT] at 0 .. 255, A[2 stages][8 steps][2 tiles][8] at 256 .. 511.
+// Lane l of quarter q holds output column  64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8
+// of the slab.  All mbarrier waits are bounded (tc_ptx.cuh).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace awq {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kWtBN = 256, kWtBK = 128;
+constexpr int kWtRing = 4;
+constexpr int kWtWBytes = kWtBK * (kWtBN / kPack) * 4;  // 16384
+constexpr int kWtRedPitch = kWtBN + 8;                  // floats
+constexpr int kWtCvWarps = 16;
+constexpr int kWtIssueWarp = kWtCvWarps, kWtProducerWarp = kWtCvWarps + 1;
+constexpr int kWtThreads = 32 * (kWtCvWarps + 2);  // 576
+constexpr int kWtTmemCols = 512;
+constexpr int kWtColA = 256;  // + (stage parity * 8 + step) * 16 + tile * 8
+
+template <int NT>
+struct WtCfg {
+  static constexpr int kXBytes = NT * kWtBK * 2;  // two [NT x 64] boxes
+  static constexpr int kStageBytes = kWtWBytes + kXBytes;
+  static constexpr int kRingBytes = kWtRing * kStageBytes;
+  static constexpr int kRedBytes = NT * kWtRedPitch * 4;
+  static constexpr int kSmemBytes = (kRingBytes > kRedBytes ? kRingBytes : kRedBytes) + 256 + 1024;
+};
+
+struct WtParams {
+  const __half* scales;
+  const uint32_t* qzeros;
+  const __half* bias;
+  __half* out;
+  int M, N, K;
+};
+
+__device__ __forceinline__ uint32_t wt_lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void wt_tmem_st(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                           uint32_t r3) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr),
+               "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ void wt_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void wt_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ __half2 dup_lo(uint32_t v) { return as_half2(prmt(v, v, 0x1010)); }
+__device__ __forceinline__ __half2 dup_hi(uint32_t v) { return as_half2(prmt(v, v, 0x3232)); }
+
+template <int NT>
+__global__ void __launch_bounds__(kWtThreads, 1)
+gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const WtParams p) {
+  using C = WtCfg<NT>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ volatile int s_abort;
+  __shared__ uint32_t s_tmem_base;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int S = (int)cluster.num_blocks();
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  float* red = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+  const uint32_t bar_base =
+      smem_base + (C::kRingBytes > C::kRedBytes ? C::kRingBytes : C::kRedBytes);
+  auto raw_full = [&](int s) { return bar_base + 8 * s; };
+  auto raw_empty = [&](int s) { return bar_base + 8 * (kWtRing + s); };
+  auto a_full = [&](int par) { return bar_base + 8 * (2 * kWtRing + par); };
+  auto a_empty = [&](int par) { return bar_base + 8 * (2 * kWtRing + 2 + par); };
+  const uint32_t d_full = bar_base + 8 * (2 * kWtRing + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int words = p.N / kPack;
+  const int word0 = blockIdx.y * (kWtBN / kPack);
+  const int m0 = blockIdx.z * NT;
+  const int KT = p.K / kWtBK;
+  const int st_begin = (int)(((long long)rank * KT) / S);
+  const int st_end = (int)(((long long)(rank + 1) * KT) / S);
+  const int nst = st_end - st_begin;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kWtRing; ++s) {
+      mbar_init(raw_full(s), 1);
+      mbar_init(raw_empty(s), kWtCvWarps + 1);  // conversion warps + the issuer's commit
+    }
+    for (int par = 0; par < 2; ++par) {
+      mbar_init(a_full(par), kWtCvWarps * 32);  // every conversion thread, once per stage
+      mbar_init(a_empty(par), 1);
+    }
+    mbar_init(d_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  if (warp == kWtProducerWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)kWtTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+
+  if (warp == kWtProducerWarp) {
+    // ------------------------------------------------------------------ producer: TMA
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      bool ok = true;
+      for (int j = 0; j < nst && ok; ++j) {
+        const int s = j % kWtRing;
+        if (j >= kWtRing)
+          ok = mbar_wait(raw_empty(s), (uint32_t)((j / kWtRing - 1) & 1), &s_abort, 31);
+        if (!ok) break;
+        const uint32_t dst = smem_base + s * C::kStageBytes;
+        const int k0 = (st_begin + j) * kWtBK;
+        mbar_arrive_expect_tx(raw_full(s), C::kStageBytes);
+        tma_load_2d(dst, &map_w, word0, k0, raw_full(s));
+        tma_load_2d(dst + kWtWBytes, &map_x, k0, m0, raw_full(s));
+        tma_load_2d(dst + kWtWBytes + NT * 128, &map_x, k0 + 64, m0, raw_full(s));
+      }
+    }
+  } else if (warp == kWtIssueWarp) {
+    // ------------------------------------------------------------------ MMA issue
+    // D fp32, A/B fp16, both K-major, N = NT tokens, M = 128 weight columns.  The whole warp
+    // runs the loop converged, one elected lane issues; operands are kept warp-uniform.
+    constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | (8u << 24);
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t ring_u = __shfl_sync(0xffffffffu, smem_base, 0);
+    bool ok = true;
+    int s = 0;
+    uint32_t ring_phase = 0;
+    // Every wait costs this warp ~100 cycles of latency even when the phase is complete, so
+    // there are two per stage (x tile landed, A half converted), and both are taken for stage
+    // j + 1 before the last MMAs of stage j are issued: they overlap with running MMAs.
+    if (nst > 0) {
+      ok = mbar_wait(raw_full(0), 0, &s_abort, 32);
+      if (ok) ok = mbar_wait(a_full(0), 0, &s_abort, 33);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    for (int j = 0; j < nst && ok; ++j) {
+      const uint32_t xt = ring_u + s * C::kStageBytes + kWtWBytes;
+      const int par = j & 1;
+      int sn = s + 1;
+      uint32_t phase_n = ring_phase;
+      if (sn == kWtRing) {
+        sn = 0;
+        phase_n ^= 1u;
+      }
+      auto issue = [&](int first, int last) {  // 16-row steps [first, last] of the stage
+#pragma unroll
+        for (int step = 0; step < 8; ++step) {
+          if (step < first || step > last) continue;
+          const uint64_t db = make_desc(xt + (step >> 2) * (NT * 128), 16, 1024) +
+                              (uint64_t)(((step & 3) * 32) >> 4);
+          const uint32_t acc = (j > 0 || step > 0) ? 1u : 0u;
+          const uint32_t acol = tmem_u + kWtColA + (par * 8 + step) * 16;
+          wt_umma_ts(tmem_u, acol, db, idesc, acc);
+          wt_umma_ts(tmem_u + NT, acol + 8, db, idesc, acc);
+        }
+      };
+      tc_fence_after();
+      if (elect_one()) issue(0, 5);
+      __syncwarp();
+      if (j + 1 < nst) {
+        ok = mbar_wait(raw_full(sn), phase_n, &s_abort, 32);
+        if (ok) ok = mbar_wait(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1), &s_abort, 33);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (elect_one()) {
+        issue(6, 7);
+        umma_commit(a_empty(par));
+        umma_commit(raw_empty(s));  // x tile of the stage read
+      }
+      __syncwarp();
+      s = sn;
+      ring_phase = phase_n;
+    }
+    if (ok && elect_one()) umma_commit(d_full);
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ conversion warps
+    const int g = lane >> 2, t = lane & 3;
+    const int q = warp & 3, r = warp >> 2;
+    const uint32_t lane_q = (uint32_t)(q * 32) << 16;
+    // raw tile as TMA leaves it: row k at k * 128, 16-byte chunk c at position c ^ (k % 8).
+    // This lane reads word 8 q + g of rows 16 step + 4 t + rr.
+    const int chunk_id = 2 * q + (g >> 2);
+    uint32_t off[4];
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      const int row = 4 * t + rr;
+      off[rr] = (uint32_t)(row * 128 + ((chunk_id ^ (row & 7)) << 4) + (g & 3) * 4);
+    }
+    const int conv_word = min(word0 + 8 * q + g, words - 1);
+    const uint32_t* zp = p.qzeros + (size_t)st_begin * words + conv_word;
+    const uint4* sp = reinterpret_cast<const uint4*>(p.scales + (size_t)st_begin * p.N) + conv_word;
+    const size_t spitch = (size_t)p.N / 8;
+    // scale / zero rows are fetched two stages ahead (registers) and six ahead (L2)
+    uint32_t zw_n = 0, zw_n2 = 0;
+    uint4 sv_n = make_uint4(0, 0, 0, 0), sv_n2 = sv_n;
+    if (nst > 0) {
+      zw_n = __ldg(zp);
+      sv_n = __ldg(sp);
+    }
+    if (nst > 1) {
+      zw_n2 = __ldg(zp + words);
+      sv_n2 = __ldg(sp + spitch);
+    }
+
+    bool ok = true;
+    for (int j = 0; j < nst && ok; ++j) {
+      const int s = j % kWtRing;
+      const uint32_t wsm = smem_base + s * C::kStageBytes;
+      // zero point and scale of this lane's eight columns for the group (= stage):
+      // zu/su[i] belong to column 2 i, zv/sv[i] to column 2 i + 1, duplicated over (k, k + 1).
+      // Odd i keep the nibble in place (1024 + 16 q): their zero is 1024 + 16 z, their scale s / 16.
+      __half2 zu[4], zv[4], su[4], sv[4];
+      {
+        const uint32_t zw = zw_n;
+        const uint4 sc = sv_n;
+        zw_n = zw_n2;
+        sv_n = sv_n2;
+        if (j + 2 < nst) {
+          zw_n2 = __ldg(zp + (size_t)(j + 2) * words);
+          sv_n2 = __ldg(sp + (size_t)(j + 2) * spitch);
+          if (t == 0) {
+            const int jp = min(j + 6, nst - 1);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(zp + (size_t)jp * words));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + (size_t)jp * spitch));
+          }
+        }
+        const uint32_t uz = prmt(zw, zw, 0x1010), vz = prmt(zw, zw, 0x3232);
+        zu[0] = as_half2(lop3_and_or(uz, 0x000F000Fu, 0x64006400u));
+        zv[0] = as_half2(lop3_and_or(vz, 0x000F000Fu, 0x64006400u));
+        zu[1] = as_half2(lop3_and_or(uz, 0x00F000F0u, 0x64006400u));
+        zv[1] = as_half2(lop3_and_or(vz, 0x00F000F0u, 0x64006400u));
+        zu[2] = as_half2(lop3_and_or(uz >> 8, 0x000F000Fu, 0x64006400u));
+        zv[2] = as_half2(lop3_and_or(vz >> 8, 0x000F000Fu, 0x64006400u));
+        zu[3] = as_half2(lop3_and_or(uz >> 8, 0x00F000F0u, 0x64006400u));
+        zv[3] = as_half2(lop3_and_or(vz >> 8, 0x00F000F0u, 0x64006400u));
+        const __half2 r16 = __float2half2_rn(0.0625f);
+        su[0] = dup_lo(sc.x);
+        sv[0] = dup_hi(sc.x);
+        su[1] = __hmul2(dup_lo(sc.y), r16);
+        sv[1] = __hmul2(dup_hi(sc.y), r16);
+        su[2] = dup_lo(sc.z);
+        sv[2] = dup_hi(sc.z);
+        su[3] = __hmul2(dup_lo(sc.w), r16);
+        sv[3] = __hmul2(dup_hi(sc.w), r16);
+      }
+      ok = mbar_wait(raw_full(s), (uint32_t)((j / kWtRing) & 1), &s_abort, 34);
+      if (!ok) break;
+      // the MMAs of stage j - 2 must have read this half of the A ring
+      if (j >= 2) ok = mbar_wait(a_empty(j & 1), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 35);
+      if (!ok) break;
+      tc_fence_after();
+      // both steps' packed words first: the loads must not queue up behind the tcgen05.st of
+      // the first step
+      uint32_t w[2][4];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const uint32_t rowA = wsm + (16 * (2 * r + e)) * 128;
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) w[e][rr] = wt_lds32(rowA + off[rr]);
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int step = 2 * r + e;
+        const uint32_t u0 = prmt(w[e][0], w[e][1], 0x5410), v0 = prmt(w[e][0], w[e][1], 0x7632);
+        const uint32_t u1 = prmt(w[e][2], w[e][3], 0x5410), v1 = prmt(w[e][2], w[e][3], 0x7632);
+        const uint32_t u0h = u0 >> 8, v0h = v0 >> 8, u1h = u1 >> 8, v1h = v1 >> 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t mask = (i & 1) ? 0x00F000F0u : 0x000F000Fu;
+          const uint32_t su0 = (i & 2) ? u0h : u0, sv0 = (i & 2) ? v0h : v0;
+          const uint32_t su1 = (i & 2) ? u1h : u1, sv1 = (i & 2) ? v1h : v1;
+          // (col 2i: k 4t..4t+1 | 4t+2..4t+3), (col 2i+1: same); (q - z) exact, then the scale
+          const uint32_t r0 = as_u32(__hmul2(
+              __hsub2(as_half2(lop3_and_or(su0, mask, 0x64006400u)), zu[i]), su[i]));
+          const uint32_t r1 = as_u32(__hmul2(
+              __hsub2(as_half2(lop3_and_or(su1, mask, 0x64006400u)), zu[i]), su[i]));
+          const uint32_t r2 = as_u32(__hmul2(
+              __hsub2(as_half2(lop3_and_or(sv0, mask, 0x64006400u)), zv[i]), sv[i]));
+          const uint32_t r3 = as_u32(__hmul2(
+              __hsub2(as_half2(lop3_and_or(sv1, mask, 0x64006400u)), zv[i]), sv[i]));
+          // half-quarter i & 1 of this warp's lanes, weight tile i >> 1
+          wt_tmem_st(tmem + lane_q + ((uint32_t)((i & 1) * 16) << 16) + kWtColA +
+                         ((j & 1) * 8 + step) * 16 + (i >> 1) * 8,
+                     r0, r1, r2, r3);
+        }
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(a_full(j & 1));
+      // every lane's reads of the stage were consumed by the conversion above
+      __syncwarp();
+      if (lane == 0) mbar_arrive(raw_empty(s));
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    // warp (q, r): its lane quarter, tokens [r NT / 4, (r + 1) NT / 4) of both tiles ->
+    // red[token][column of the slab] (aliases the ring: d_full implies every stage was
+    // converted and read by the tensor core)
+    if (ok && nst > 0) ok = mbar_wait(d_full, 0, &s_abort, 36);
+    if (ok) {
+      tc_fence_after();
+      const int hp = lane >> 4, odd = (lane >> 3) & 1, gp = lane & 7;
+      constexpr int kTok = NT / 4;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int nl = 64 * q + 8 * gp + 2 * (2 * u + hp) + odd;
+#pragma unroll
+        for (int c0 = 0; c0 < kTok; c0 += 16) {
+          uint32_t d[16];
+          if (nst > 0) {
+            wt_tmem_ld16(tmem + lane_q + (uint32_t)(u * NT + r * kTok + c0), d);
+          } else {
+#pragma unroll
+            for (int m = 0; m < 16; ++m) d[m] = 0u;
+          }
+#pragma unroll
+          for (int m = 0; m < 16; ++m)
+            red[(r * kTok + c0 + m) * kWtRedPitch + nl] = __uint_as_float(d[m]);
+        }
+      }
+    }
+  }
+
+  // ---- reduction over the cluster ranks through distributed shared memory ----
+  tc_fence_before();
+  __syncthreads();
+  cluster.sync();
+  if (!s_abort) {
+    constexpr int kUnits = kWtBN / 8;
+    const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
+    const int nun = uend - ubeg;
+    const int n_slab = blockIdx.y * kWtBN;
+    for (int idx = tid; idx < nun * NT; idx += kWtThreads) {
+      const int u = ubeg + idx % nun, ml = idx / nun;
+      const int n = n_slab + u * 8, m = m0 + ml;
+      if (m >= p.M || n >= p.N) continue;
+      float v[8];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) v[jj] = 0.f;
+      for (int rk = 0; rk < S; ++rk) {
+        const float* peer = cluster.map_shared_rank(red, rk) + ml * kWtRedPitch + u * 8;
+        const float4 a = *reinterpret_cast<const float4*>(peer);
+        const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
+      if (p.bias != nullptr) {
+        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+        const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) v[jj] += __half2float(bh[jj]);
+      }
+      __align__(16) __half o[8];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) o[jj] = __float2half_rn(v[jj]);
+      *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+  cluster.sync();
+
+  // ---- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kWtProducerWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                 "r"((uint32_t)kWtTmemCols)
+                 : "memory");
+  }
+}
+
+template <int NT>
+int launch_wt(const uint32_t* qweight, const __half* x, const WtParams& p, cudaStream_t stream) {
+  using C = WtCfg<NT>;
+  CUtensorMap map_w, map_x;
+  // packed weights [K rows][N / 8 words], box [128 rows x 32 words], 128-byte swizzle
+  if (int rc = encode_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight,
+                             (uint64_t)(p.N / kPack), (uint64_t)p.K, (uint64_t)(p.N / kPack) * 4,
+                             kWtBN / kPack, kWtBK, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  // activations [M rows][K], box [NT tokens x 64 k] (rows past M read as zero), 128-byte swizzle
+  if (int rc = encode_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)p.K,
+                             (uint64_t)p.M, (uint64_t)p.K * 2, 64, NT, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  auto kernel = gemm_wt_kernel<NT>;
+  if (!attr_done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::kSmemBytes) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+    attr_done[dev] = true;
+  }
+  const int slabs = (p.N + kWtBN - 1) / kWtBN;
+  const int mtiles = (p.M + NT - 1) / NT;
+  const int KT = p.K / kWtBK;
+  // cluster size (K split): only when the tiles alone leave SMs idle (one CTA per SM, and a
+  // cluster has to find all its SMs free at once, which costs more than it gains otherwise)
+  const int slots = sm_count();
+  const int tiles = slabs * mtiles;
+  int S = 1;
+  if (tiles < slots) {
+    S = slots / tiles;
+    S = S > 8 ? 8 : S;
+    while (S > 1 && KT / S < 4) --S;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S, slabs, mtiles);
+  cfg.blockDim = dim3(kWtThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, p) != cudaSuccess) {
+    cudaGetLastError();
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
+}
+
+}  // namespace
+
+bool gemm_wt_supported(int M, int N, int K, int group) {
+  // N % 32: 16-byte TMA row pitch of the packed weights; K % 128: whole stages = whole groups
+  return M >= 1 && N % 32 == 0 && K % kWtBK == 0 && group == 128;
+}
+
+int launch_gemm_wt(const __half* x, const uint32_t* qweight, const __half* scales,
+                   const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
+                   int group, cudaStream_t stream) {
+  if (!gemm_wt_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+  WtParams p{scales, qzeros, bias, out, M, N, K};
+  return M <= 64 ? launch_wt<64>(qweight, x, p, stream) : launch_wt<128>(qweight, x, p, stream);
+}
+
+int wt_device_status(int* out) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
+  *out = v;
+  return AWQ_B200_OK;
+}
+
+}  // namespace awq
