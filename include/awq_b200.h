@@ -63,7 +63,7 @@ int awq_b200_dequantize(const void* qweight, const void* scales, const void* qze
  * Replaces torch.ops._C.awq_gemm(input, qweight, scales, qzeros, split_k_iters)
  * (vllm/_custom_ops.py:576-587; called from quantization/awq.py:283) and the
  * awq_dequantize + torch.matmul pair used for >= 256 tokens (awq.py:276-281): one entry
- * point serves every M, picking a weight-streaming kernel or a tcgen05 kernel by M.
+ * point serves every M, picking a weight-streaming kernel or one of the tcgen05 kernels by M.
  * `kernel` selects the implementation: AWQ_B200_KERNEL_AUTO or one of the explicit ids (a
  * request the shape does not permit returns AWQ_B200_ERR_SHAPE).
  * Scratch: awq_b200_gemm_workspace_bytes(M, N, K, group, kernel) bytes, 256-byte aligned; may

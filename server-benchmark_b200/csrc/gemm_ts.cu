@@ -7,22 +7,26 @@
 // not fed to mma.sync: they are written to tensor memory with tcgen05.st.16x256b and become the
 // A operand (128 weight columns x 16 k) of tcgen05.mma.kind::f16; the activations are the small
 // B operand ([16 tokens x 64 k] K-major, 128-byte swizzle) in shared memory.  The dequantised
-// weights never touch shared memory and the 5th-generation tensor core does the arithmetic.
+// weights never touch shared memory, the 5th-generation tensor core does the arithmetic, and the
+// conversion warps execute nothing but the unpack (one instruction per weight).
 //
-// The CTA is a pipeline of specialised warps joined by mbarrier rings (slab of 256 output
-// columns = two 128-lane A tiles; stage = 128 weight rows = one quantisation group; K range
-// split over a thread-block cluster as in gemm_stream.cu):
+// One CTA per SM (all 512 TMEM columns); slab of 256 output columns = two interleaved 128-lane A
+// tiles (tile u = columns 4u..4u+3 of every packed word); stage = 128 weight rows = one
+// quantisation group; K range split over a thread-block cluster when the slabs alone would
+// leave SMs idle.  Roles, joined by mbarrier rings:
 //
-//   producer (1 thread)   TMA: packed weights [128 rows x 128 B] + x [16 tokens x 128 k] of a
-//                         stage into a 5-deep shared-memory ring            raw_full / raw_empty
-//   conversion (8 warps)  warp (q, p): TMEM lane quarter q, quarter-stages c = p and p + 2.
-//                         Per quarter-stage (two 16-row steps): ld.shared -> unpack ->
-//                         8 x tcgen05.st into A slot c                      a_full[c] / done0, done1
-//   issue (1 warp)        converged warp, one elected lane: per 16-row step one MMA per A tile
-//                         (weight tile 0, weight tile 1, constant tile) into the group
-//                         accumulators D[b]; two tcgen05.commit per stage   done0, done1[b] / d_empty[b]
-//   fold (4 warps)        warp q: tcgen05.ld its lanes of D[b];
-//                         tot += scale * (acc - zero * sum_x) in fp32 registers
+//   producer (1 thread)    TMA: packed weights [128 rows x 128 B] + x [16 tokens x 128 k] of a
+//                          stage into a 6-deep ring                          raw_full / raw_empty
+//   conversion (16 warps)  warp (q, h, par): TMEM lane quarter q, 16-row steps 4h .. 4h + 3 of
+//                          the stages of parity par: ld.shared -> unpack -> tcgen05.st into the
+//                          A ring.  The ring holds two stages and each parity has its own
+//                          warps, so the conversions of consecutive stages overlap and run
+//                          ahead of the MMAs                                 a_full / done
+//   issue (1 warp)         converged warp, one elected lane: per step one MMA per A tile (weight
+//                          tile 0, weight tile 1, constant tile) into the group accumulators
+//                          D[b]                                              done[b] / d_empty[b]
+//   fold (4 warps)         warp q: tcgen05.ld its lanes of D[b];
+//                          tot += scale * (acc - zero * sum_x) in fp32 registers
 //
 // The constant tile (every k slot = 2^-24) yields sum_k x per token in the same scaling as the
 // weight tiles, so the zero point is applied per group without a separate reduction.
@@ -32,17 +36,15 @@
 //     its warp parked at a barrier) costs that lane 45 to 270 cycles depending on how its
 //     operands are computed; issued from a converged warp under elect.sync with warp-uniform
 //     operands it costs ~23 (M = 128, N = 16, K = 16, A in TMEM);
-//   * a tcgen05.commit drains the tensor pipe (~75 cycles in which no MMA starts): with one
-//     commit per A slot and per consumer the pipe spent half its time drained, hence two
-//     commits per stage and barriers shared by every consumer of the same event;
-//   * every mbarrier wait costs its warp ~100 cycles even when the phase is already complete.
-// What bounds the kernel now is that TMEM holds only one stage of A next to the accumulators
-// (256 columns per CTA, two CTAs per SM): conversion of stage j + 1 cannot start before the MMAs
-// of stage j have read the slot, so conversion and MMA latencies add up instead of overlapping.
+//   * every mbarrier wait costs its warp ~100 cycles even when the phase is already complete,
+//     so the issuing warp probes the barriers of stage j + 1 before the last MMAs of stage j;
+//   * with two CTAs per SM (256 TMEM columns each) only one stage of A fits next to the
+//     accumulators, conversion of stage j + 1 then waits for the MMAs of stage j and the
+//     latencies add up (2.1 - 2.5 TB/s); hence one CTA per SM and a two-stage A ring.
 //
-// TMEM columns (256 allocated, two CTAs per SM): D[2 buffers][3 tiles][16] = 96,
-// A[4 quarter-stage slots][2 tiles][2 steps][8] = 128, constant tile 8.  Lane l of quarter q holds
-// output column  64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8  of the slab.
+// TMEM columns: D[2 buffers][3 tiles][16] at 0 .. 95, constant tile at 96 .. 103,
+// A[2 stages][8 steps][2 tiles][8] at 256 .. 511.  Lane l of quarter q holds output column
+//   64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8      of the slab.
 //
 // All mbarrier waits are bounded (tc_ptx.cuh); a wait that runs out aborts the CTA cleanly.
 #include <cooperative_groups.h>
@@ -60,22 +62,21 @@ using namespace tc;
 
 constexpr int kTsBN = 256, kTsBK = 128;
 constexpr int kNT = 16;                         // tokens padded to the MMA's N
-constexpr int kRing = 5;                        // stages in flight
+constexpr int kRing = 6;                        // stages in flight
 constexpr int kTsWBytes = kTsBK * (kTsBN / kPack) * 4;  // 16384
 constexpr int kTsXBytes = kNT * kTsBK * 2;              // 4096: two [16 x 64] tiles
 constexpr int kTsStageBytes = kTsWBytes + kTsXBytes;    // 20480
-constexpr int kTsRingBytes = kRing * kTsStageBytes;     // 102400
+constexpr int kTsRingBytes = kRing * kTsStageBytes;     // 122880
 constexpr int kTsRedPitch = kTsBN + 8;                  // floats
-constexpr int kTsBarBytes = 256;
-constexpr int kTsSmemBytes = kTsRingBytes + kTsBarBytes + 1024;  // + alignment slack
-constexpr int kCvWarps = 8, kFoldWarps = 4;
+constexpr int kTsSmemBytes = kTsRingBytes + 256 + 1024;  // + barriers + alignment slack
+constexpr int kCvWarps = 16, kFoldWarps = 4;
 constexpr int kFoldWarp0 = kCvWarps, kIssueWarp = kCvWarps + kFoldWarps;
 constexpr int kProducerWarp = kIssueWarp + 1;
-constexpr int kTsThreads = 32 * (kProducerWarp + 1);  // 448
-constexpr int kTmemColsTs = 256;
+constexpr int kTsThreads = 32 * (kProducerWarp + 1);  // 704
+constexpr int kTmemColsTs = 512;
 constexpr int kColD = 0;      // + buffer * 48 + tile * 16
-constexpr int kColA = 96;     // + slot * 32 + tile * 16 + step * 8
-constexpr int kColOnes = 224;
+constexpr int kColOnes = 96;
+constexpr int kColA = 256;    // + (stage parity * 8 + step) * 16 + tile * 8
 static_assert(kNT * kTsRedPitch * 4 <= kTsRingBytes, "partial tile must fit the idle ring");
 
 struct TsParams {
@@ -97,6 +98,15 @@ __device__ __forceinline__ void tmem_st_16x256b(uint32_t taddr, uint32_t r0, uin
                "r"(r0), "r"(r1), "r"(r2), "r"(r3)
                : "memory");
 }
+// four adjacent 8-column groups in one instruction (x4): registers 4 c .. 4 c + 3 go to group c
+__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
@@ -110,14 +120,13 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(
-          tmem_d),
-      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
 template <bool EXACT>
-__global__ void __launch_bounds__(kTsThreads, 2)
+__global__ void __launch_bounds__(kTsThreads, 1)
 gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const TsParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -133,10 +142,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t bar_base = smem_base + kTsRingBytes;
   auto raw_full = [&](int s) { return bar_base + 8 * s; };
   auto raw_empty = [&](int s) { return bar_base + 8 * (kRing + s); };
-  auto a_full = [&](int c) { return bar_base + 8 * (2 * kRing + c); };
-  auto done0 = [&]() { return bar_base + 8 * (2 * kRing + 4); };
-  auto done1 = [&](int b) { return bar_base + 8 * (2 * kRing + 5 + b); };
-  auto d_empty = [&](int b) { return bar_base + 8 * (2 * kRing + 7 + b); };
+  auto a_full = [&](int par) { return bar_base + 8 * (2 * kRing + par); };
+  auto done = [&](int par) { return bar_base + 8 * (2 * kRing + 2 + par); };
+  auto d_empty = [&](int par) { return bar_base + 8 * (2 * kRing + 4 + par); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int words = p.N / kPack;
@@ -150,14 +158,12 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     s_abort = 0;
     for (int s = 0; s < kRing; ++s) {
       mbar_init(raw_full(s), 1);
-      mbar_init(raw_empty(s), kCvWarps);
+      mbar_init(raw_empty(s), kCvWarps / 2 + 1);  // the stage's conversion warps + the issuer's commit
     }
-    for (int c = 0; c < 4; ++c)
-      mbar_init(a_full(c), 4 * 32);  // the four warps (one per lane quarter) that fill slot c
-    mbar_init(done0(), 1);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(done1(b), 1);
-      mbar_init(d_empty(b), kFoldWarps * 32);
+    for (int par = 0; par < 2; ++par) {
+      mbar_init(a_full(par), kCvWarps / 2 * 32);  // the conversion threads of that stage parity
+      mbar_init(done(par), 1);                // commit after the MMAs of a stage
+      mbar_init(d_empty(par), kFoldWarps * 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -194,55 +200,72 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   } else if (warp == kIssueWarp) {
     // ------------------------------------------------------------------ MMA issue
-    // The whole warp runs the loop and stays converged; one elected lane issues (see elect_one).
-    // Two commits per stage: done0 after the first half (A slots 0, 1 free again) and done1[b]
-    // at the end (A slots 2, 3 free, D[b] complete, x tile of the stage read).
-    // D fp32, A/B fp16, both K-major, N = 16 tokens, M = 128 weight columns
+    // D fp32, A/B fp16, both K-major, N = 16 tokens, M = 128 weight columns.  The whole warp
+    // runs the loop converged, one elected lane issues; the operands are computed from
+    // warp-uniform values only (broadcast bases, wrapping counters instead of divisions).
     constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kNT >> 3) << 17) | (8u << 24);
-    // Operands of tcgen05 instructions live in uniform registers: keep everything they are
-    // computed from provably warp-uniform (broadcast bases, wrapping counters instead of
-    // divisions), otherwise every MMA pays for moving its operands across register files.
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
     const uint32_t ring_u = __shfl_sync(0xffffffffu, smem_base, 0);
     bool ok = true;
     int s = 0;
     uint32_t ring_phase = 0;
-    for (int j = 0; j < nst && ok; ++j) {
-      const int b = j & 1;
-      if (j >= 2) ok = mbar_wait(d_empty(b), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 11);
-      if (ok) ok = mbar_wait(raw_full(s), ring_phase, &s_abort, 12);
+    if (nst > 0) {
+      ok = mbar_wait(raw_full(0), 0, &s_abort, 11);
+      if (ok) ok = mbar_wait(a_full(0), 0, &s_abort, 12);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    }
+    for (int j = 0; j < nst && ok; ++j) {
       const uint32_t xt = ring_u + s * kTsStageBytes + kTsWBytes;
-      const uint32_t dcol = tmem_u + kColD + b * 48;
+      const int par = j & 1;
+      const uint32_t dcol = tmem_u + kColD + par * 48;
+      int sn = s + 1;
+      uint32_t phase_n = ring_phase;
+      if (sn == kRing) {
+        sn = 0;
+        phase_n ^= 1u;
+      }
+      auto issue = [&](int first, int last) {  // 16-row steps [first, last] of the stage
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        // slot c converted (the constant tile was written before the first a_full[0])
-        ok = mbar_wait(a_full(c), (uint32_t)(j & 1), &s_abort, 13);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        if (elect_one()) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int step = 2 * c + e;
-            const uint64_t db = make_desc(xt + (step >> 2) * 2048, 16, 1024) +
-                                (uint64_t)(((step & 3) * 32) >> 4);
-            const uint32_t acc = step == 0 ? 0u : 1u;
-            const uint32_t acol = tmem_u + kColA + c * 32 + e * 8;
-            umma_f16_ts(dcol, acol, db, idesc, acc);
-            umma_f16_ts(dcol + 16, acol + 16, db, idesc, acc);
-            if (!EXACT) umma_f16_ts(dcol + 32, tmem_u + kColOnes, db, idesc, acc);
-          }
-          if (c == 1) umma_commit(done0());
-          if (c == 3) umma_commit(done1(b));
+        for (int step = 0; step < 8; ++step) {
+          if (step < first || step > last) continue;
+          const uint64_t db = make_desc(xt + (step >> 2) * 2048, 16, 1024) +
+                              (uint64_t)(((step & 3) * 32) >> 4);
+          const uint32_t acc = step == 0 ? 0u : 1u;
+          const uint32_t acol = tmem_u + kColA + (par * 8 + step) * 16;
+          umma_f16_ts(dcol, acol, db, idesc, acc);
+          umma_f16_ts(dcol + 16, acol + 8, db, idesc, acc);
+          if (!EXACT) umma_f16_ts(dcol + 32, tmem_u + kColOnes, db, idesc, acc);
         }
-        __syncwarp();
+      };
+      tc_fence_after();
+      if (elect_one()) issue(0, 5);
+      __syncwarp();
+      // What stage j + 1 needs is probed while the MMAs just issued run (a wait costs ~100
+      // cycles even when the phase is complete).  The probe must not block: the commit of
+      // stage j below is what lets the conversion of stage j + 2 start.
+      bool ready = true;
+      if (j + 1 < nst) {
+        ready = mbar_test(raw_full(sn), phase_n);
+        ready &= mbar_test(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1));
+        // D[par ^ 1] was last used by stage j - 1: its sums must have been folded
+        if (j >= 1) ready &= mbar_test(d_empty(par ^ 1), (uint32_t)((((j + 1) >> 1) - 1) & 1));
+        ready = __all_sync(0xffffffffu, ready);
       }
-      if (++s == kRing) {
-        s = 0;
-        ring_phase ^= 1u;
+      if (elect_one()) {
+        issue(6, 7);
+        umma_commit(done(par));      // A half par free again, D[par] complete
+        umma_commit(raw_empty(s));   // x tile of the stage read
       }
+      __syncwarp();
+      if (!ready) {
+        ok = mbar_wait(raw_full(sn), phase_n, &s_abort, 11);
+        if (ok) ok = mbar_wait(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1), &s_abort, 12);
+        if (ok && j >= 1)
+          ok = mbar_wait(d_empty(par ^ 1), (uint32_t)((((j + 1) >> 1) - 1) & 1), &s_abort, 13);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      s = sn;
+      ring_phase = phase_n;
     }
   } else if (warp >= kFoldWarp0) {
     // ------------------------------------------------------------------ fold
@@ -259,28 +282,42 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     const __half* sp = p.scales + (size_t)st_begin * p.N + fold_word * 8;
     const uint32_t* zp = p.qzeros + (size_t)st_begin * words + fold_word;
-    __half s0n = __float2half(0.f), s1n = s0n;
-    uint32_t zwn = 0;
+    // scale / zero of the next two groups in registers, of a few more in L2
+    __half s0n = __float2half(0.f), s1n = s0n, s0n2 = s0n, s1n2 = s0n;
+    uint32_t zwn = 0, zwn2 = 0;
     if (nst > 0) {
       s0n = __ldg(sp + col0);
       s1n = __ldg(sp + col1);
       zwn = __ldg(zp);
+    }
+    if (nst > 1) {
+      s0n2 = __ldg(sp + (size_t)p.N + col0);
+      s1n2 = __ldg(sp + (size_t)p.N + col1);
+      zwn2 = __ldg(zp + words);
     }
     bool ok = true;
     for (int j = 0; j < nst && ok; ++j) {
       const int b = j & 1;
       const float s0 = __half2float(s0n), s1 = __half2float(s1n);
       const uint32_t zw = zwn;
-      if (j + 1 < nst) {
-        s0n = __ldg(sp + (size_t)(j + 1) * p.N + col0);
-        s1n = __ldg(sp + (size_t)(j + 1) * p.N + col1);
-        zwn = __ldg(zp + (size_t)(j + 1) * words);
+      s0n = s0n2;
+      s1n = s1n2;
+      zwn = zwn2;
+      if (j + 2 < nst) {
+        s0n2 = __ldg(sp + (size_t)(j + 2) * p.N + col0);
+        s1n2 = __ldg(sp + (size_t)(j + 2) * p.N + col1);
+        zwn2 = __ldg(zp + (size_t)(j + 2) * words);
+        if (odd == 0 && hp == 0) {
+          const int jp = min(j + 6, nst - 1);
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + (size_t)jp * p.N));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(zp + (size_t)jp * words));
+        }
       }
       // odd half-quarters hold nibbles kept in place (16 q), so their zero point is 16 z
       const float zf = hp ? 16.f : 1.f;
       const float z0 = zf * (float)((zw >> (4 * nib0)) & 0xF);
       const float z1 = zf * (float)((zw >> (4 * nib1)) & 0xF);
-      ok = mbar_wait(done1(b), (uint32_t)((j >> 1) & 1), &s_abort, 14);
+      ok = mbar_wait(done(b), (uint32_t)((j >> 1) & 1), &s_abort, 14);
       if (!ok) break;
       tc_fence_after();
       const uint32_t dcol = tmem + lane_q + kColD + b * 48;
@@ -309,7 +346,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     // ---- partial tile to shared memory: red[token][column of the slab] (the ring is idle:
-    //      the last done1 implies every stage was converted and read by the tensor core) ----
+    //      the last done implies every stage was converted and read by the tensor core) ----
     if (ok) {
       const float f = EXACT ? 1.f : (hp ? 1048576.f : 16777216.f);  // undo 2^-20 / 2^-24
       const int nl0 = 64 * q + 8 * gp + col0, nl1 = 64 * q + 8 * gp + col1;
@@ -321,38 +358,42 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ conversion warps
+    // Warp (q, h, par): TMEM lane quarter q, steps 4 h .. 4 h + 3 of the stages of parity par.
+    // A warp's own chain of waits, loads, unpack and TMEM stores takes longer than a stage
+    // lasts; with the two parities on different warps the chains of consecutive stages overlap.
     const int g = lane >> 2, t = lane & 3;
-    const int q = warp & 3, par = warp >> 2;
+    const int q = warp & 3, h = (warp >> 2) & 1, par = warp >> 3;
     const uint32_t lane_q = (uint32_t)(q * 32) << 16;
-    // raw tile as TMA leaves it: row r at r * 128, 16-byte chunk c at position c ^ (r % 8).
-    // This lane reads word 8 q + g of rows 16 s + 4 t + rr.
+    // raw tile as TMA leaves it: row k at k * 128, 16-byte chunk c at position c ^ (k % 8).
+    // This lane reads word 8 q + g of rows 16 step + 4 t + rr.
     const int chunk_id = 2 * q + (g >> 2);
     uint32_t off[4];
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
-      const int r = 4 * t + rr;
-      off[rr] = (uint32_t)(r * 128 + ((chunk_id ^ (r & 7)) << 4) + (g & 3) * 4);
+      const int row = 4 * t + rr;
+      off[rr] = (uint32_t)(row * 128 + ((chunk_id ^ (row & 7)) << 4) + (g & 3) * 4);
     }
     const int conv_word = min(word0 + 8 * q + g, words - 1);
 
-    if (!EXACT && par == 0) {
-      // constant A tile: every k slot of every lane = 2^-24 (fp16 subnormal 0x0001)
+    if (!EXACT && h == 0 && par == 0) {
+      // constant A tile: every k slot of every lane = 2^-24 (fp16 subnormal 0x0001); complete
+      // before this warp's first arrival on a_full[0]
       tmem_st_16x256b(tmem + lane_q + kColOnes, 0x00010001u, 0x00010001u, 0x00010001u, 0x00010001u);
       tmem_st_16x256b(tmem + lane_q + (16u << 16) + kColOnes, 0x00010001u, 0x00010001u,
                       0x00010001u, 0x00010001u);
     }
     uint32_t zw_n = 0;
-    if (EXACT && nst > 0) zw_n = __ldg(p.qzeros + (size_t)st_begin * words + conv_word);
+    if (EXACT && par < nst) zw_n = __ldg(p.qzeros + (size_t)(st_begin + par) * words + conv_word);
 
     bool ok = true;
-    for (int j = 0; j < nst && ok; ++j) {
+    for (int j = par; j < nst && ok; j += 2) {
       const int s = j % kRing;
       const uint32_t wsm = smem_base + s * kTsStageBytes;
       // EXACT: zero registers of this thread's packed word for the group (= stage)
       __half2 zu[4], zv[4];
       if (EXACT) {
         const uint32_t zw = zw_n;
-        if (j + 1 < nst) zw_n = __ldg(p.qzeros + (size_t)(st_begin + j + 1) * words + conv_word);
+        if (j + 2 < nst) zw_n = __ldg(p.qzeros + (size_t)(st_begin + j + 2) * words + conv_word);
         const uint32_t uz = prmt(zw, zw, 0x1010), vz = prmt(zw, zw, 0x3232);
         const __half2 m16 = __float2half2_rn(-0.0625f);
         zu[0] = as_half2(lop3_and_or(uz, 0x000F000Fu, 0x64006400u));
@@ -366,32 +407,29 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       ok = mbar_wait(raw_full(s), (uint32_t)((j / kRing) & 1), &s_abort, 15);
       if (!ok) break;
+      // all four steps' packed words first: the loads must not queue up behind tcgen05.st
+      uint32_t w[4][4];
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = par + 2 * cc;  // quarter-stage = A slot
-        // slot c of the previous stage must have been read by the tensor core
-        if (j >= 1) {
-          if (cc == 0) {
-            ok = mbar_wait(done0(), (uint32_t)((j - 1) & 1), &s_abort, 16);
-          } else {
-            ok = mbar_wait(done1((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), &s_abort, 17);
-            // the previous stage is finished with: this warp's reads of its packed weights were
-            // consumed by the conversion, the tensor core has read its x tile
-            __syncwarp();
-            if (ok && lane == 0) mbar_arrive(raw_empty((j - 1) % kRing));
-          }
-        }
-        if (!ok) break;
-        tc_fence_after();
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t rowA = wsm + (16 * (4 * h + e)) * 128;
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) w[e][rr] = lds32(rowA + off[rr]);
+      }
+      // the MMAs of stage j - 2 must have read this half of the A ring
+      if (j >= 2) ok = mbar_wait(done(par), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 16);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int sp = 0; sp < 2; ++sp) {
+        // fragments of two steps: frag[hq][4 * (2 e + tile) + k] -- the two tiles of a step and
+        // two consecutive steps are adjacent column groups of the A ring, so one x4 store per
+        // half-quarter writes all four
+        uint32_t frag[2][16];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const uint32_t rowA = wsm + (16 * (2 * c + e)) * 128;
-          const uint32_t w0 = lds32(rowA + off[0]);
-          const uint32_t w1 = lds32(rowA + off[1]);
-          const uint32_t w2 = lds32(rowA + off[2]);
-          const uint32_t w3 = lds32(rowA + off[3]);
-          const uint32_t u0 = prmt(w0, w1, 0x5410), v0 = prmt(w0, w1, 0x7632);
-          const uint32_t u1 = prmt(w2, w3, 0x5410), v1 = prmt(w2, w3, 0x7632);
+          const uint32_t* ww = w[2 * sp + e];
+          const uint32_t u0 = prmt(ww[0], ww[1], 0x5410), v0 = prmt(ww[0], ww[1], 0x7632);
+          const uint32_t u1 = prmt(ww[2], ww[3], 0x5410), v1 = prmt(ww[2], ww[3], 0x7632);
           const uint32_t u0h = u0 >> 8, v0h = v0 >> 8, u1h = u1 >> 8, v1h = v1 >> 8;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -423,19 +461,28 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               r3 = sv1 & mask;
             }
             // half-quarter i & 1 of this warp's lanes, weight tile i >> 1
-            tmem_st_16x256b(tmem + lane_q + ((uint32_t)((i & 1) * 16) << 16) + kColA + c * 32 +
-                                (i >> 1) * 16 + e * 8,
-                            r0, r1, r2, r3);
+            const int c = 4 * (2 * e + (i >> 1));
+            frag[i & 1][c] = r0;
+            frag[i & 1][c + 1] = r1;
+            frag[i & 1][c + 2] = r2;
+            frag[i & 1][c + 3] = r3;
           }
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        tc_fence_before();
-        mbar_arrive(a_full(c));
+        const uint32_t a_slot = tmem + lane_q + kColA + (par * 8 + 4 * h + 2 * sp) * 16;
+        tmem_st_16x256b_x4(a_slot, frag[0]);
+        tmem_st_16x256b_x4(a_slot + (16u << 16), frag[1]);
       }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(a_full(par));
+      // every lane's reads of the stage were consumed by the conversion above
+      __syncwarp();
+      if (lane == 0) mbar_arrive(raw_empty(s));
     }
   }
 
   // ---- reduction over the cluster ranks through distributed shared memory ----
+  tc_fence_before();
   __syncthreads();
   cluster.sync();
   if (!s_abort) {
@@ -450,8 +497,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       float v[8];
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) v[jj] = 0.f;
-      for (int r = 0; r < S; ++r) {
-        const float* peer = cluster.map_shared_rank(red, r) + m * kTsRedPitch + u * 8;
+      for (int rk = 0; rk < S; ++rk) {
+        const float* peer = cluster.map_shared_rank(red, rk) + m * kTsRedPitch + u * 8;
         const float4 a = *reinterpret_cast<const float4*>(peer);
         const float4 b = *reinterpret_cast<const float4*>(peer + 4);
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
@@ -498,18 +545,14 @@ int launch_ts(const CUtensorMap& map_w, const CUtensorMap& map_x, const TsParams
   }
   const int slabs = (p.N + kTsBN - 1) / kTsBN;
   const int KT = p.K / kTsBK;
-  // cluster size (K split): the one that needs the least time in units of a whole-K CTA,
-  // rounds of 2 CTAs per SM times 1 / S; ties go to the smaller cluster
-  const int slots = 2 * sm_count();
+  // cluster size (K split): only when the slabs alone leave SMs idle (one CTA per SM, and a
+  // cluster has to find all its SMs free at once, which costs more than it gains otherwise)
+  const int slots = sm_count();
   int S = 1;
-  double best = 1e30;
-  for (int s = 1; s <= 8 && KT / s >= 4; ++s) {
-    const int rounds = (slabs * s + slots - 1) / slots;
-    const double cost = (double)rounds / s + 0.02 * s;
-    if (cost < best) {
-      best = cost;
-      S = s;
-    }
+  if (slabs < slots) {
+    S = slots / slabs;
+    S = S > 8 ? 8 : S;
+    while (S > 1 && KT / S < 4) --S;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S, slabs, 1);

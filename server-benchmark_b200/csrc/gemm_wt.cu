@@ -192,8 +192,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int s = 0;
     uint32_t ring_phase = 0;
     // Every wait costs this warp ~100 cycles of latency even when the phase is complete, so
-    // there are two per stage (x tile landed, A half converted), and both are taken for stage
-    // j + 1 before the last MMAs of stage j are issued: they overlap with running MMAs.
+    // there are two per stage (x tile landed, A half converted), and both are probed for stage
+    // j + 1 before the last MMAs of stage j are issued.
     if (nst > 0) {
       ok = mbar_wait(raw_full(0), 0, &s_abort, 32);
       if (ok) ok = mbar_wait(a_full(0), 0, &s_abort, 33);
@@ -223,10 +223,13 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       tc_fence_after();
       if (elect_one()) issue(0, 5);
       __syncwarp();
+      // What stage j + 1 needs is probed while the MMAs just issued run.  The probe must not
+      // block: the commit of stage j below is what lets the conversion of stage j + 2 start.
+      bool ready = true;
       if (j + 1 < nst) {
-        ok = mbar_wait(raw_full(sn), phase_n, &s_abort, 32);
-        if (ok) ok = mbar_wait(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1), &s_abort, 33);
-        ok = __all_sync(0xffffffffu, ok);
+        ready = mbar_test(raw_full(sn), phase_n);
+        ready &= mbar_test(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1));
+        ready = __all_sync(0xffffffffu, ready);
       }
       if (elect_one()) {
         issue(6, 7);
@@ -234,6 +237,11 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         umma_commit(raw_empty(s));  // x tile of the stage read
       }
       __syncwarp();
+      if (!ready) {
+        ok = mbar_wait(raw_full(sn), phase_n, &s_abort, 32);
+        if (ok) ok = mbar_wait(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1), &s_abort, 33);
+        ok = __all_sync(0xffffffffu, ok);
+      }
       s = sn;
       ring_phase = phase_n;
     }
