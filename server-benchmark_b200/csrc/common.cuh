@@ -133,6 +133,12 @@ int launch_gemm_wt(const __half* x, const uint32_t* qweight, const __half* scale
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, cudaStream_t stream);
 int wt_device_status(int* out);
+bool moe_wt_supported(int H, int I, int group);
+int launch_wt_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
+                      const __half* scales, const uint32_t* qzeros, const float* topk_weights,
+                      const int32_t* sorted_ids, const int32_t* expert_ids,
+                      const int32_t* num_post_pad, __half* out, int numel, int K, int N, int group,
+                      int half_cols, int nblk, cudaStream_t stream);
 
 int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                         int renormalize, float* topk_weights, int32_t* topk_ids,

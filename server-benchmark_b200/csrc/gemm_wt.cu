@@ -27,6 +27,13 @@
 //   epilogue               the conversion warps: tcgen05.ld -> fp32 partial tile in shared
 //                          memory -> sum over the cluster ranks through DSMEM -> fp16 (+ bias)
 //
+// MODE 0 is the dense linear.  MODE 1 / 2 are the grouped expert GEMMs of a fused-MoE layer on
+// the permuted token list (moe_align_kernel with block = NT): row block b belongs to expert
+// expert_ids[b]; padding tokens only widen the B operand, so they cost no weight work.
+//   MODE 1  gate_up: the slab's first 128 columns are gate columns, the other 128 the matching
+//           up columns; epilogue act[pos, c] = silu(gate) * up.
+//   MODE 2  down: epilogue pair_out[flat pair id, c] = routed weight * D.
+//
 // TMEM columns: D[2 tiles][NT] at 0 .. 255, A[2 stages][8 steps][2 tiles][8] at 256 .. 511.
 // Lane l of quarter q holds output column  64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8
 // of the slab.  All mbarrier waits are bounded (tc_ptx.cuh).
@@ -68,6 +75,13 @@ struct WtParams {
   const __half* bias;
   __half* out;
   int M, N, K;
+  // grouped modes
+  const float* topk_weights;   // [numel] routed weights (MODE 2)
+  const int32_t* sorted_ids;   // permuted flat (token, slot) ids, padding = numel
+  const int32_t* expert_ids;   // expert of every NT-row block
+  const int32_t* num_post_pad;
+  int numel;                   // tokens * topk
+  int half_cols;               // MODE 1: I (gate columns [0, I), up columns [I, 2 I))
 };
 
 __device__ __forceinline__ uint32_t wt_lds32(uint32_t addr) {
@@ -104,7 +118,7 @@ __device__ __forceinline__ void wt_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uin
 __device__ __forceinline__ __half2 dup_lo(uint32_t v) { return as_half2(prmt(v, v, 0x1010)); }
 __device__ __forceinline__ __half2 dup_hi(uint32_t v) { return as_half2(prmt(v, v, 0x3232)); }
 
-template <int NT>
+template <int NT, int MODE>
 __global__ void __launch_bounds__(kWtThreads, 1)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const WtParams p) {
@@ -129,9 +143,27 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int words = p.N / kPack;
-  const int word0 = blockIdx.y * (kWtBN / kPack);
   const int m0 = blockIdx.z * NT;
   const int KT = p.K / kWtBK;
+  // The slab's packed words come as two boxes of 16 words: [w_left, +16) and [w_right, +16).
+  int w_left, w_right, wrow0 = 0, grp0 = 0;
+  if (MODE == 0) {
+    w_left = blockIdx.y * (kWtBN / kPack);
+    w_right = w_left + 16;
+  } else {
+    if (m0 >= p.num_post_pad[0]) return;  // block past the permuted list (whole CTA, cluster of 1)
+    const int e = p.expert_ids[blockIdx.z];
+    if (e < 0) return;
+    wrow0 = e * p.K;
+    grp0 = e * KT;
+    if (MODE == 1) {
+      w_left = blockIdx.y * 16;
+      w_right = p.half_cols / kPack + blockIdx.y * 16;
+    } else {
+      w_left = blockIdx.y * (kWtBN / kPack);
+      w_right = w_left + 16;
+    }
+  }
   const int st_begin = (int)(((long long)rank * KT) / S);
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
   const int nst = st_end - st_begin;
@@ -176,7 +208,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t dst = smem_base + s * C::kStageBytes;
         const int k0 = (st_begin + j) * kWtBK;
         mbar_arrive_expect_tx(raw_full(s), C::kStageBytes);
-        tma_load_2d(dst, &map_w, word0, k0, raw_full(s));
+        tma_load_2d(dst, &map_w, w_left, wrow0 + k0, raw_full(s));
+        tma_load_2d(dst + kWtWBytes / 2, &map_w, w_right, wrow0 + k0, raw_full(s));
         tma_load_2d(dst + kWtWBytes, &map_x, k0, m0, raw_full(s));
         tma_load_2d(dst + kWtWBytes + NT * 128, &map_x, k0 + 64, m0, raw_full(s));
       }
@@ -252,18 +285,21 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int g = lane >> 2, t = lane & 3;
     const int q = warp & 3, r = warp >> 2;
     const uint32_t lane_q = (uint32_t)(q * 32) << 16;
-    // raw tile as TMA leaves it: row k at k * 128, 16-byte chunk c at position c ^ (k % 8).
-    // This lane reads word 8 q + g of rows 16 step + 4 t + rr.
-    const int chunk_id = 2 * q + (g >> 2);
+    // raw tile as TMA leaves it: two boxes of [128 rows x 64 B] (64-byte swizzle): row k of box
+    // q / 2 at k * 64, 16-byte chunk c at position c ^ ((k / 2) % 4).
+    // This lane reads word 8 (q % 2) + g of that box, rows 16 step + 4 t + rr.
+    const int chunk_id = 2 * (q & 1) + (g >> 2);
     uint32_t off[4];
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
       const int row = 4 * t + rr;
-      off[rr] = (uint32_t)(row * 128 + ((chunk_id ^ (row & 7)) << 4) + (g & 3) * 4);
+      off[rr] = (uint32_t)((q >> 1) * (kWtWBytes / 2) + row * 64 +
+                           ((chunk_id ^ ((row >> 1) & 3)) << 4) + (g & 3) * 4);
     }
-    const int conv_word = min(word0 + 8 * q + g, words - 1);
-    const uint32_t* zp = p.qzeros + (size_t)st_begin * words + conv_word;
-    const uint4* sp = reinterpret_cast<const uint4*>(p.scales + (size_t)st_begin * p.N) + conv_word;
+    const int conv_word = min(((q >> 1) ? w_right : w_left) + 8 * (q & 1) + g, words - 1);
+    const uint32_t* zp = p.qzeros + (size_t)(grp0 + st_begin) * words + conv_word;
+    const uint4* sp =
+        reinterpret_cast<const uint4*>(p.scales + (size_t)(grp0 + st_begin) * p.N) + conv_word;
     const size_t spitch = (size_t)p.N / 8;
     // scale / zero rows are fetched two stages ahead (registers) and six ahead (L2)
     uint32_t zw_n = 0, zw_n2 = 0;
@@ -329,7 +365,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       uint32_t w[2][4];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const uint32_t rowA = wsm + (16 * (2 * r + e)) * 128;
+        const uint32_t rowA = wsm + (16 * (2 * r + e)) * 64;
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) w[e][rr] = wt_lds32(rowA + off[rr]);
       }
@@ -401,34 +437,66 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   cluster.sync();
   if (!s_abort) {
-    constexpr int kUnits = kWtBN / 8;
-    const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
-    const int nun = uend - ubeg;
-    const int n_slab = blockIdx.y * kWtBN;
-    for (int idx = tid; idx < nun * NT; idx += kWtThreads) {
-      const int u = ubeg + idx % nun, ml = idx / nun;
-      const int n = n_slab + u * 8, m = m0 + ml;
-      if (m >= p.M || n >= p.N) continue;
-      float v[8];
+    if (MODE == 0) {
+      constexpr int kUnits = kWtBN / 8;
+      const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
+      const int nun = uend - ubeg;
+      const int n_slab = blockIdx.y * kWtBN;
+      for (int idx = tid; idx < nun * NT; idx += kWtThreads) {
+        const int u = ubeg + idx % nun, ml = idx / nun;
+        const int n = n_slab + u * 8, m = m0 + ml;
+        if (m >= p.M || n >= p.N) continue;
+        float v[8];
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) v[jj] = 0.f;
-      for (int rk = 0; rk < S; ++rk) {
-        const float* peer = cluster.map_shared_rank(red, rk) + ml * kWtRedPitch + u * 8;
-        const float4 a = *reinterpret_cast<const float4*>(peer);
-        const float4 b = *reinterpret_cast<const float4*>(peer + 4);
-        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+        for (int jj = 0; jj < 8; ++jj) v[jj] = 0.f;
+        for (int rk = 0; rk < S; ++rk) {
+          const float* peer = cluster.map_shared_rank(red, rk) + ml * kWtRedPitch + u * 8;
+          const float4 a = *reinterpret_cast<const float4*>(peer);
+          const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+          v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+          v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+        }
+        if (p.bias != nullptr) {
+          const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+          const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) v[jj] += __half2float(bh[jj]);
+        }
+        __align__(16) __half o[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) o[jj] = __float2half_rn(v[jj]);
+        *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = *reinterpret_cast<uint4*>(o);
       }
-      if (p.bias != nullptr) {
-        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-        const __half* bh = reinterpret_cast<const __half*>(&bv);
+    } else if (MODE == 1) {
+      // act[pos, 128 slab + c] = silu(gate) * up; gate = red[.][c], up = red[.][128 + c]
+      for (int idx = tid; idx < 16 * NT; idx += kWtThreads) {
+        const int u = idx % 16, ml = idx / 16;
+        const int c = blockIdx.y * 128 + u * 8;
+        if (c >= p.half_cols) continue;
+        const float* gp = red + ml * kWtRedPitch + u * 8;
+        __align__(16) __half o[8];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) v[jj] += __half2float(bh[jj]);
+        for (int jj = 0; jj < 8; ++jj) {
+          const float gv = gp[jj];
+          o[jj] = __float2half_rn(gv / (1.f + __expf(-gv)) * gp[128 + jj]);
+        }
+        *reinterpret_cast<uint4*>(p.out + (size_t)(m0 + ml) * p.half_cols + c) =
+            *reinterpret_cast<uint4*>(o);
       }
-      __align__(16) __half o[8];
+    } else {
+      // pair_out[flat pair id, 256 slab + c] = routed weight * D
+      for (int idx = tid; idx < 32 * NT; idx += kWtThreads) {
+        const int u = idx % 32, ml = idx / 32;
+        const int n = blockIdx.y * kWtBN + u * 8;
+        const int fid = p.sorted_ids[m0 + ml];
+        if (fid >= p.numel || n >= p.N) continue;
+        const float rw = __ldg(p.topk_weights + fid);
+        const float* src = red + ml * kWtRedPitch + u * 8;
+        __align__(16) __half o[8];
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) o[jj] = __float2half_rn(v[jj]);
-      *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = *reinterpret_cast<uint4*>(o);
+        for (int jj = 0; jj < 8; ++jj) o[jj] = __float2half_rn(src[jj] * rw);
+        *reinterpret_cast<uint4*>(p.out + (size_t)fid * p.N + n) = *reinterpret_cast<uint4*>(o);
+      }
     }
   }
   cluster.sync();
@@ -444,45 +512,23 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
-template <int NT>
-int launch_wt(const uint32_t* qweight, const __half* x, const WtParams& p, cudaStream_t stream) {
+template <int NT, int MODE>
+int launch_wt_kernel(const CUtensorMap& map_w, const CUtensorMap& map_x, const WtParams& p, dim3 grid,
+                     int S, cudaStream_t stream) {
   using C = WtCfg<NT>;
-  CUtensorMap map_w, map_x;
-  // packed weights [K rows][N / 8 words], box [128 rows x 32 words], 128-byte swizzle
-  if (int rc = encode_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight,
-                             (uint64_t)(p.N / kPack), (uint64_t)p.K, (uint64_t)(p.N / kPack) * 4,
-                             kWtBN / kPack, kWtBK, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
-  // activations [M rows][K], box [NT tokens x 64 k] (rows past M read as zero), 128-byte swizzle
-  if (int rc = encode_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)p.K,
-                             (uint64_t)p.M, (uint64_t)p.K * 2, 64, NT, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
-  auto kernel = gemm_wt_kernel<NT>;
+  auto kernel = gemm_wt_kernel<NT, MODE>;
   if (!attr_done[dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::kSmemBytes) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
   }
-  const int slabs = (p.N + kWtBN - 1) / kWtBN;
-  const int mtiles = (p.M + NT - 1) / NT;
-  const int KT = p.K / kWtBK;
-  // cluster size (K split): only when the tiles alone leave SMs idle (one CTA per SM, and a
-  // cluster has to find all its SMs free at once, which costs more than it gains otherwise)
-  const int slots = sm_count();
-  const int tiles = slabs * mtiles;
-  int S = 1;
-  if (tiles < slots) {
-    S = slots / tiles;
-    S = S > 8 ? 8 : S;
-    while (S > 1 && KT / S < 4) --S;
-  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(S, slabs, mtiles);
+  cfg.gridDim = grid;
   cfg.blockDim = dim3(kWtThreads, 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
@@ -500,6 +546,38 @@ int launch_wt(const uint32_t* qweight, const __half* x, const WtParams& p, cudaS
   return AWQ_B200_OK;
 }
 
+// packed weights [rows][N / 8 words], box [128 rows x 16 words], 64-byte swizzle;
+// activations [a_rows][K], box [NT tokens x 64 k] (rows past the end read as zero), 128-byte swizzle
+int make_wt_maps(CUtensorMap* map_w, CUtensorMap* map_x, const uint32_t* qweight, int64_t wrows,
+                 int N, const __half* x, int64_t a_rows, int K, int nt) {
+  if (int rc = encode_map_2d(map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, (uint64_t)(N / kPack),
+                             (uint64_t)wrows, (uint64_t)(N / kPack) * 4, 16, kWtBK,
+                             CU_TENSOR_MAP_SWIZZLE_64B))
+    return rc;
+  return encode_map_2d(map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)K, (uint64_t)a_rows,
+                       (uint64_t)K * 2, 64, (uint32_t)nt, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <int NT>
+int launch_wt(const uint32_t* qweight, const __half* x, const WtParams& p, cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  if (int rc = make_wt_maps(&map_w, &map_x, qweight, p.K, p.N, x, p.M, p.K, NT)) return rc;
+  const int slabs = (p.N + kWtBN - 1) / kWtBN;
+  const int mtiles = (p.M + NT - 1) / NT;
+  const int KT = p.K / kWtBK;
+  // cluster size (K split): only when the tiles alone leave SMs idle (one CTA per SM, and a
+  // cluster has to find all its SMs free at once, which costs more than it gains otherwise)
+  const int slots = sm_count();
+  const int tiles = slabs * mtiles;
+  int S = 1;
+  if (tiles < slots) {
+    S = slots / tiles;
+    S = S > 8 ? 8 : S;
+    while (S > 1 && KT / S < 4) --S;
+  }
+  return launch_wt_kernel<NT, 0>(map_w, map_x, p, dim3(S, slabs, mtiles), S, stream);
+}
+
 }  // namespace
 
 bool gemm_wt_supported(int M, int N, int K, int group) {
@@ -511,8 +589,31 @@ int launch_gemm_wt(const __half* x, const uint32_t* qweight, const __half* scale
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, cudaStream_t stream) {
   if (!gemm_wt_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
-  WtParams p{scales, qzeros, bias, out, M, N, K};
+  WtParams p{scales, qzeros, bias, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0, 0};
   return M <= 64 ? launch_wt<64>(qweight, x, p, stream) : launch_wt<128>(qweight, x, p, stream);
+}
+
+bool moe_wt_supported(int H, int I, int group) {
+  // slabs: 128 gate + 128 up columns (I % 128), 256 hidden columns (H % 256); stage = group = 128
+  return H % 256 == 0 && I % 128 == 0 && group == 128;
+}
+
+// Grouped expert GEMM of a fused-MoE layer (MODE 1 / 2 of the kernel).  a: activations in
+// permuted row order [a_rows, K] (row blocks of 128); w: packed expert weights stacked along the
+// rows [experts * K, N / 8].
+int launch_wt_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
+                      const __half* scales, const uint32_t* qzeros, const float* topk_weights,
+                      const int32_t* sorted_ids, const int32_t* expert_ids,
+                      const int32_t* num_post_pad, __half* out, int numel, int K, int N, int group,
+                      int half_cols, int nblk, cudaStream_t stream) {
+  if (group != 128 || K % kWtBK != 0 || N % 32 != 0) return AWQ_B200_ERR_SHAPE;
+  CUtensorMap map_w, map_x;
+  if (int rc = make_wt_maps(&map_w, &map_x, w, (int64_t)experts * K, N, a, a_rows, K, 128)) return rc;
+  WtParams p{scales, qzeros, nullptr, out, (int)a_rows, N, K, topk_weights, sorted_ids,
+             expert_ids, num_post_pad, numel, half_cols};
+  if (mode == 1)
+    return launch_wt_kernel<128, 1>(map_w, map_x, p, dim3(1, half_cols / 128, nblk), 1, stream);
+  return launch_wt_kernel<128, 2>(map_w, map_x, p, dim3(1, N / kWtBN, nblk), 1, stream);
 }
 
 int wt_device_status(int* out) {

@@ -80,13 +80,17 @@ int launch_moe_experts_tc(const MoeArgs& a, void* workspace, size_t workspace_by
   moe_gather_kernel<<<(unsigned)rows, 256, 0, stream>>>(a.x, a.sorted_ids, a.num_post_pad, x_perm,
                                                         numel, a.topk, a.H);
   if (cudaGetLastError() != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
-  if (int rc = launch_tc_grouped(1, x_perm, rows, a.w13_q, a.E, a.w13_s, a.w13_z, nullptr,
-                                 a.sorted_ids, a.expert_ids, a.num_post_pad, act, numel, a.H,
-                                 2 * a.I, a.group, a.I, nblk, stream))
+  // group 128: dequantised weights in TMEM as the A operand (gemm_wt.cu), padding tokens cost no
+  // weight work there; group 64: weights dequantised into a shared-memory B tile (gemm_tc.cu)
+  const bool wt = moe_wt_supported(a.H, a.I, a.group);
+  auto grouped = wt ? launch_wt_grouped : launch_tc_grouped;
+  if (int rc = grouped(1, x_perm, rows, a.w13_q, a.E, a.w13_s, a.w13_z, nullptr, a.sorted_ids,
+                       a.expert_ids, a.num_post_pad, act, numel, a.H, 2 * a.I, a.group, a.I, nblk,
+                       stream))
     return rc;
-  if (int rc = launch_tc_grouped(2, act, rows, a.w2_q, a.E, a.w2_s, a.w2_z, a.topk_weights,
-                                 a.sorted_ids, a.expert_ids, a.num_post_pad, pair_out, numel, a.I,
-                                 a.H, a.group, 0, nblk, stream))
+  if (int rc = grouped(2, act, rows, a.w2_q, a.E, a.w2_s, a.w2_z, a.topk_weights, a.sorted_ids,
+                       a.expert_ids, a.num_post_pad, pair_out, numel, a.I, a.H, a.group, 0, nblk,
+                       stream))
     return rc;
   return launch_moe_sum(pair_out, a.out, a.T, a.topk, a.H, stream);
 }
