@@ -133,9 +133,11 @@ def test_fused_experts_vs_oracle(A, e, h, i, t, k):
     assert O.rel_err(y2, ref) < TOL
 
 
-def test_fused_experts_expert_parallel_shards_sum(A):
-    """Two expert-parallel shards (expert_map) add up to the unsharded layer."""
-    e, h, i, t, k = 8, 256, 128, 20, 2
+@pytest.mark.parametrize("t", [20, 400])
+def test_fused_experts_expert_parallel_shards_sum(A, t):
+    """Two expert-parallel shards (expert_map) add up to the unsharded layer (T = 20: streaming
+    kernels, T = 400: grouped tcgen05 GEMMs with blocks of experts that live on another rank)."""
+    e, h, i, k = 8, 256, 128, 2
     w1, w2, x, logits = _moe_case(e, h, i, t, k, seed=77)
     w, ids, _ = O.topk_softmax(logits.numpy(), k, True)
     wt, idt = torch.from_numpy(w).cuda(), torch.from_numpy(ids).cuda()
