@@ -161,9 +161,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(raw_empty(s), kCvWarps / 2 + 1);  // the stage's conversion warps + the issuer's commit
     }
     for (int par = 0; par < 2; ++par) {
-      mbar_init(a_full(par), kCvWarps / 2 * 32);  // the conversion threads of that stage parity
+      mbar_init(a_full(par), kCvWarps / 2);   // one arrival per conversion warp of that parity
       mbar_init(done(par), 1);                // commit after the MMAs of a stage
-      mbar_init(d_empty(par), kFoldWarps * 32);
+      mbar_init(d_empty(par), kFoldWarps);    // one arrival per fold warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -329,8 +329,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (!EXACT) tmem_ld8(dcol + 32 + th * 8, dx);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (th == 1) {
+          // one arrival per warp: 128 arrivals on one shared-memory word serialise
           tc_fence_before();
-          mbar_arrive(d_empty(b));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(d_empty(b));
         }
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
@@ -474,10 +476,13 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
-      mbar_arrive(a_full(par));
-      // every lane's reads of the stage were consumed by the conversion above
+      // every lane's TMEM stores are complete and its reads of the stage were consumed; one
+      // arrival per warp (hundreds of arrivals on one shared-memory word would serialise)
       __syncwarp();
-      if (lane == 0) mbar_arrive(raw_empty(s));
+      if (lane == 0) {
+        mbar_arrive(a_full(par));
+        mbar_arrive(raw_empty(s));
+      }
     }
   }
 

@@ -175,7 +175,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(raw_empty(s), kWtCvWarps + 1);  // conversion warps + the issuer's commit
     }
     for (int par = 0; par < 2; ++par) {
-      mbar_init(a_full(par), kWtCvWarps * 32);  // every conversion thread, once per stage
+      mbar_init(a_full(par), kWtCvWarps);  // one arrival per conversion warp and stage
       mbar_init(a_empty(par), 1);
     }
     mbar_init(d_full, 1);
@@ -397,10 +397,13 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
-      mbar_arrive(a_full(j & 1));
-      // every lane's reads of the stage were consumed by the conversion above
+      // every lane's TMEM stores are complete and its reads of the stage were consumed; one
+      // arrival per warp (hundreds of arrivals on one shared-memory word would serialise)
       __syncwarp();
-      if (lane == 0) mbar_arrive(raw_empty(s));
+      if (lane == 0) {
+        mbar_arrive(a_full(j & 1));
+        mbar_arrive(raw_empty(s));
+      }
     }
 
     // ---------------------------------------------------------------- epilogue
