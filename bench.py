@@ -360,9 +360,8 @@ def run_cuda(args):
                        "l2": "inputs larger than L2 (438.8 MB of weights per step)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         "kernel": "gemm_stream_kernel<MT=2> (gate_up) + gemm_ts_kernel (qkv, "
-                                   "o_proj, down); step = 4 launches, achieved = weight bytes "
-                                   "of the step / step time",
+                         "kernel": "gemm_ts_kernel (4 launches per step: qkv, o_proj, gate_up, "
+                                   "down); achieved = weight bytes of the step / step time",
                          "achieved_all_bytes": achieved_all,
                          "traffic": NCU_TRAFFIC_RATIO * all_bytes_per_step(m) / launches_per_step},
             "cpu_baseline": cpu,

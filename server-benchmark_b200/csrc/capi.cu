@@ -30,9 +30,7 @@ int check_awq_shape(int N, int K, int group) {
 
 // Kernel choice for AWQ_B200_KERNEL_AUTO (measured crossovers on B200, Qwen2.5-72B shapes):
 //   M <= 8                      mma.sync streaming kernel (one 8-token tile: 4 TB/s)
-//   M <= 16                     tcgen05 with weights in TMEM (gemm_ts) unless the 256-column
-//                               slabs outnumber the SMs (one CTA per SM there: the second,
-//                               partial wave costs more than the streaming kernel loses)
+//   M <= 16                     tcgen05 with the unpacked weights in TMEM (gemm_ts)
 //   M <= 128, or M <= 256 and   dequantised weights in TMEM as the A operand (gemm_wt)
 //   fewer tiles than SMs
 //   larger M                    tcgen05 with the weights dequantised into shared memory
@@ -41,7 +39,7 @@ int pick_gemm_kernel(int M, int N, int K, int group) {
   const int slabs = (N + 255) / 256;
   if (M <= 8 && awq::gemm_stream_supported(M, N, K, group)) return AWQ_B200_KERNEL_STREAM;
   if (M <= 16) {
-    if (slabs < sms && awq::gemm_ts_supported(M, N, K, group)) return AWQ_B200_KERNEL_TS;
+    if (awq::gemm_ts_supported(M, N, K, group)) return AWQ_B200_KERNEL_TS;
     if (awq::gemm_stream_supported(M, N, K, group)) return AWQ_B200_KERNEL_STREAM;
   }
   if (awq::gemm_wt_supported(M, N, K, group) &&

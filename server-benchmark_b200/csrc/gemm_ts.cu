@@ -19,9 +19,9 @@
 //                          stage into a 6-deep ring                          raw_full / raw_empty
 //   conversion (16 warps)  warp (q, h, par): TMEM lane quarter q, 16-row steps 4h .. 4h + 3 of
 //                          the stages of parity par: ld.shared -> unpack -> tcgen05.st into the
-//                          A ring.  The ring holds two stages and each parity has its own
+//                          A ring.  The ring holds three stages and each parity has its own
 //                          warps, so the conversions of consecutive stages overlap and run
-//                          ahead of the MMAs                                 a_full / done
+//                          ahead of the MMAs                                 a_full / a_empty
 //   issue (1 warp)         converged warp, one elected lane: per step one MMA per A tile (weight
 //                          tile 0, weight tile 1, constant tile) into the group accumulators
 //                          D[b]                                              done[b] / d_empty[b]
@@ -40,10 +40,12 @@
 //     so the issuing warp probes the barriers of stage j + 1 before the last MMAs of stage j;
 //   * with two CTAs per SM (256 TMEM columns each) only one stage of A fits next to the
 //     accumulators, conversion of stage j + 1 then waits for the MMAs of stage j and the
-//     latencies add up (2.1 - 2.5 TB/s); hence one CTA per SM and a two-stage A ring.
+//     latencies add up (2.1 - 2.5 TB/s); hence one CTA per SM and a three-stage A ring: the
+//     chain  slot free -> convert -> issue -> MMAs complete  (~2100 cycles) has three stage
+//     times to close.
 //
 // TMEM columns: D[2 buffers][3 tiles][16] at 0 .. 95, constant tile at 96 .. 103,
-// A[2 stages][8 steps][2 tiles][8] at 256 .. 511.  Lane l of quarter q holds output column
+// A[3 stages][8 steps][2 tiles][8] at 128 .. 511.  Lane l of quarter q holds output column
 //   64 q + 8 (l % 8) + 2 (2 tile + l / 16) + (l % 16) / 8      of the slab.
 //
 // All mbarrier waits are bounded (tc_ptx.cuh); a wait that runs out aborts the CTA cleanly.
@@ -76,7 +78,8 @@ constexpr int kTsThreads = 32 * (kProducerWarp + 1);  // 704
 constexpr int kTmemColsTs = 512;
 constexpr int kColD = 0;      // + buffer * 48 + tile * 16
 constexpr int kColOnes = 96;
-constexpr int kColA = 256;    // + (stage parity * 8 + step) * 16 + tile * 8
+constexpr int kASlots = 3;     // stages of A held in TMEM
+constexpr int kColA = 128;    // + (slot * 8 + step) * 16 + tile * 8
 static_assert(kNT * kTsRedPitch * 4 <= kTsRingBytes, "partial tile must fit the idle ring");
 
 struct TsParams {
@@ -142,9 +145,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t bar_base = smem_base + kTsRingBytes;
   auto raw_full = [&](int s) { return bar_base + 8 * s; };
   auto raw_empty = [&](int s) { return bar_base + 8 * (kRing + s); };
-  auto a_full = [&](int par) { return bar_base + 8 * (2 * kRing + par); };
-  auto done = [&](int par) { return bar_base + 8 * (2 * kRing + 2 + par); };
-  auto d_empty = [&](int par) { return bar_base + 8 * (2 * kRing + 4 + par); };
+  auto a_full = [&](int slot) { return bar_base + 8 * (2 * kRing + slot); };
+  auto a_empty = [&](int slot) { return bar_base + 8 * (2 * kRing + 3 + slot); };
+  auto done = [&](int par) { return bar_base + 8 * (2 * kRing + 6 + par); };
+  auto d_empty = [&](int par) { return bar_base + 8 * (2 * kRing + 8 + par); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int words = p.N / kPack;
@@ -154,20 +158,38 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
   const int nst = st_end - st_begin;
 
-  if (tid == 0) {
+  auto load_stage = [&](int j) {  // producer thread: TMA loads of local stage j
+    const int s = j % kRing;
+    const uint32_t dst = smem_base + s * kTsStageBytes;
+    const int k0 = (st_begin + j) * kTsBK;
+    mbar_arrive_expect_tx(raw_full(s), kTsStageBytes);
+    tma_load_2d(dst, &map_w, word0, k0, raw_full(s));
+    tma_load_2d(dst + kTsWBytes, &map_x, k0, 0, raw_full(s));
+    tma_load_2d(dst + kTsWBytes + 2048, &map_x, k0 + 64, 0, raw_full(s));
+  };
+  if (warp == kProducerWarp && lane == 0) {
+    // this thread sets the barriers up and has the first stages in flight before anyone else
+    // is through the prologue (the first TMA round trip is the longest latency of a short CTA)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     s_abort = 0;
     for (int s = 0; s < kRing; ++s) {
       mbar_init(raw_full(s), 1);
       mbar_init(raw_empty(s), kCvWarps / 2 + 1);  // the stage's conversion warps + the issuer's commit
     }
+    for (int slot = 0; slot < kASlots; ++slot) {
+      mbar_init(a_full(slot), kCvWarps / 2);  // one arrival per conversion warp of the stage
+      mbar_init(a_empty(slot), 1);            // commit after the MMAs that read the slot
+    }
     for (int par = 0; par < 2; ++par) {
-      mbar_init(a_full(par), kCvWarps / 2);   // one arrival per conversion warp of that parity
-      mbar_init(done(par), 1);                // commit after the MMAs of a stage
+      mbar_init(done(par), 1);                // commit after the MMAs of a stage: D[par] complete
       mbar_init(d_empty(par), kFoldWarps);    // one arrival per fold warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
+    for (int j = 0; j < nst && j < kRing; ++j) load_stage(j);
   }
+  __syncwarp();
   if (warp == kProducerWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
@@ -182,20 +204,12 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ producer: TMA
+    // (the first kRing stages were issued in the prologue)
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       bool ok = true;
-      for (int j = 0; j < nst && ok; ++j) {
-        const int s = j % kRing;
-        if (j >= kRing) ok = mbar_wait(raw_empty(s), (uint32_t)((j / kRing - 1) & 1), &s_abort, 21);
-        if (!ok) break;
-        const uint32_t dst = smem_base + s * kTsStageBytes;
-        const int k0 = (st_begin + j) * kTsBK;
-        mbar_arrive_expect_tx(raw_full(s), kTsStageBytes);
-        tma_load_2d(dst, &map_w, word0, k0, raw_full(s));
-        tma_load_2d(dst + kTsWBytes, &map_x, k0, 0, raw_full(s));
-        tma_load_2d(dst + kTsWBytes + 2048, &map_x, k0 + 64, 0, raw_full(s));
+      for (int j = kRing; j < nst && ok; ++j) {
+        ok = mbar_wait(raw_empty(j % kRing), (uint32_t)((j / kRing - 1) & 1), &s_abort, 21);
+        if (ok) load_stage(j);
       }
     }
   } else if (warp == kIssueWarp) {
@@ -207,8 +221,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
     const uint32_t ring_u = __shfl_sync(0xffffffffu, smem_base, 0);
     bool ok = true;
-    int s = 0;
-    uint32_t ring_phase = 0;
+    int s = 0, slot = 0;               // ring slot and A slot of stage j (wrapping counters)
+    uint32_t ring_phase = 0, slot_phase = 0;
     if (nst > 0) {
       ok = mbar_wait(raw_full(0), 0, &s_abort, 11);
       if (ok) ok = mbar_wait(a_full(0), 0, &s_abort, 12);
@@ -218,11 +232,15 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const uint32_t xt = ring_u + s * kTsStageBytes + kTsWBytes;
       const int par = j & 1;
       const uint32_t dcol = tmem_u + kColD + par * 48;
-      int sn = s + 1;
-      uint32_t phase_n = ring_phase;
+      int sn = s + 1, slot_n = slot + 1;
+      uint32_t phase_n = ring_phase, slot_phase_n = slot_phase;
       if (sn == kRing) {
         sn = 0;
         phase_n ^= 1u;
+      }
+      if (slot_n == kASlots) {
+        slot_n = 0;
+        slot_phase_n ^= 1u;
       }
       auto issue = [&](int first, int last) {  // 16-row steps [first, last] of the stage
 #pragma unroll
@@ -231,7 +249,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint64_t db = make_desc(xt + (step >> 2) * 2048, 16, 1024) +
                               (uint64_t)(((step & 3) * 32) >> 4);
           const uint32_t acc = step == 0 ? 0u : 1u;
-          const uint32_t acol = tmem_u + kColA + (par * 8 + step) * 16;
+          const uint32_t acol = tmem_u + kColA + (slot * 8 + step) * 16;
           umma_f16_ts(dcol, acol, db, idesc, acc);
           umma_f16_ts(dcol + 16, acol + 8, db, idesc, acc);
           if (!EXACT) umma_f16_ts(dcol + 32, tmem_u + kColOnes, db, idesc, acc);
@@ -246,26 +264,29 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       bool ready = true;
       if (j + 1 < nst) {
         ready = mbar_test(raw_full(sn), phase_n);
-        ready &= mbar_test(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1));
+        ready &= mbar_test(a_full(slot_n), slot_phase_n);
         // D[par ^ 1] was last used by stage j - 1: its sums must have been folded
         if (j >= 1) ready &= mbar_test(d_empty(par ^ 1), (uint32_t)((((j + 1) >> 1) - 1) & 1));
         ready = __all_sync(0xffffffffu, ready);
       }
       if (elect_one()) {
         issue(6, 7);
-        umma_commit(done(par));      // A half par free again, D[par] complete
+        umma_commit(a_empty(slot));  // A slot free again
+        umma_commit(done(par));      // D[par] complete
         umma_commit(raw_empty(s));   // x tile of the stage read
       }
       __syncwarp();
       if (!ready) {
         ok = mbar_wait(raw_full(sn), phase_n, &s_abort, 11);
-        if (ok) ok = mbar_wait(a_full(par ^ 1), (uint32_t)(((j + 1) >> 1) & 1), &s_abort, 12);
+        if (ok) ok = mbar_wait(a_full(slot_n), slot_phase_n, &s_abort, 12);
         if (ok && j >= 1)
           ok = mbar_wait(d_empty(par ^ 1), (uint32_t)((((j + 1) >> 1) - 1) & 1), &s_abort, 13);
         ok = __all_sync(0xffffffffu, ok);
       }
       s = sn;
       ring_phase = phase_n;
+      slot = slot_n;
+      slot_phase = slot_phase_n;
     }
   } else if (warp >= kFoldWarp0) {
     // ------------------------------------------------------------------ fold
@@ -417,8 +438,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) w[e][rr] = lds32(rowA + off[rr]);
       }
-      // the MMAs of stage j - 2 must have read this half of the A ring
-      if (j >= 2) ok = mbar_wait(done(par), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 16);
+      // the MMAs of stage j - 3 must have read this slot of the A ring
+      const int slot = j % kASlots;
+      if (j >= kASlots)
+        ok = mbar_wait(a_empty(slot), (uint32_t)((j / kASlots - 1) & 1), &s_abort, 16);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -470,7 +493,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             frag[i & 1][c + 3] = r3;
           }
         }
-        const uint32_t a_slot = tmem + lane_q + kColA + (par * 8 + 4 * h + 2 * sp) * 16;
+        const uint32_t a_slot = tmem + lane_q + kColA + (slot * 8 + 4 * h + 2 * sp) * 16;
         tmem_st_16x256b_x4(a_slot, frag[0]);
         tmem_st_16x256b_x4(a_slot + (16u << 16), frag[1]);
       }
@@ -480,7 +503,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // arrival per warp (hundreds of arrivals on one shared-memory word would serialise)
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(a_full(par));
+        mbar_arrive(a_full(slot));
         mbar_arrive(raw_empty(s));
       }
     }
@@ -489,7 +512,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // ---- reduction over the cluster ranks through distributed shared memory ----
   tc_fence_before();
   __syncthreads();
-  cluster.sync();
+  if (S > 1) cluster.sync();  // every rank's partial tile is in its shared memory
   if (!s_abort) {
     constexpr int kUnits = kTsBN / 8;
     const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
@@ -521,7 +544,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = *reinterpret_cast<uint4*>(o);
     }
   }
-  cluster.sync();
+  if (S > 1) cluster.sync();  // peers are done reading this CTA's shared memory
 
   // ---- teardown ----
   tc_fence_before();

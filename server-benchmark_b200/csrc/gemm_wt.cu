@@ -17,9 +17,9 @@
 //
 //   producer (1 thread)    TMA: packed weights [128 rows x 128 B] + x [NT x 128 k] of a stage
 //                          into a 4-deep ring                                raw_full / raw_empty
-//   conversion (16 warps)  warp (q, r): TMEM lane quarter q, quarter-stage r (16-row steps 2r,
-//                          2r + 1) of every stage -> A slot (stage parity, r); the A ring holds
-//                          two stages, so conversion runs up to two stages ahead of the MMAs
+//   conversion (16 warps)  warp (q, h, par): TMEM lane quarter q, 16-row steps 4h .. 4h + 3 of the
+//                          stages of parity par -> A half par; the A ring holds two stages, so
+//                          conversion runs up to two stages ahead of the MMAs
 //                                                                            a_full / a_empty
 //   issue (1 warp)         converged warp, elected lane: per step one MMA per tile into
 //                          D[tile] (fp32, accumulated over the CTA's whole K range);
@@ -89,11 +89,14 @@ __device__ __forceinline__ uint32_t wt_lds32(uint32_t addr) {
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ void wt_tmem_st(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2,
-                                           uint32_t r3) {
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr),
-               "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-               : "memory");
+// four adjacent 8-column groups in one instruction (x4): registers 4 c .. 4 c + 3 go to group c
+__device__ __forceinline__ void wt_tmem_st_x4(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
 }
 __device__ __forceinline__ void wt_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -168,20 +171,36 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
   const int nst = st_end - st_begin;
 
-  if (tid == 0) {
+  auto load_stage = [&](int j) {  // producer thread: TMA loads of local stage j
+    const int s = j % kWtRing;
+    const uint32_t dst = smem_base + s * C::kStageBytes;
+    const int k0 = (st_begin + j) * kWtBK;
+    mbar_arrive_expect_tx(raw_full(s), C::kStageBytes);
+    tma_load_2d(dst, &map_w, w_left, wrow0 + k0, raw_full(s));
+    tma_load_2d(dst + kWtWBytes / 2, &map_w, w_right, wrow0 + k0, raw_full(s));
+    tma_load_2d(dst + kWtWBytes, &map_x, k0, m0, raw_full(s));
+    tma_load_2d(dst + kWtWBytes + NT * 128, &map_x, k0 + 64, m0, raw_full(s));
+  };
+  if (warp == kWtProducerWarp && lane == 0) {
+    // this thread sets the barriers up and has the first stages in flight before anyone else
+    // is through the prologue (the first TMA round trip is the longest latency of a short CTA)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     s_abort = 0;
     for (int s = 0; s < kWtRing; ++s) {
       mbar_init(raw_full(s), 1);
-      mbar_init(raw_empty(s), kWtCvWarps + 1);  // conversion warps + the issuer's commit
+      mbar_init(raw_empty(s), kWtCvWarps / 2 + 1);  // the stage's conversion warps + the issuer's commit
     }
     for (int par = 0; par < 2; ++par) {
-      mbar_init(a_full(par), kWtCvWarps);  // one arrival per conversion warp and stage
+      mbar_init(a_full(par), kWtCvWarps / 2);  // one arrival per conversion warp of that parity
       mbar_init(a_empty(par), 1);
     }
     mbar_init(d_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
+    for (int j = 0; j < nst && j < kWtRing; ++j) load_stage(j);
   }
+  __syncwarp();
   if (warp == kWtProducerWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
@@ -196,22 +215,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == kWtProducerWarp) {
     // ------------------------------------------------------------------ producer: TMA
+    // (the first kWtRing stages were issued in the prologue)
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       bool ok = true;
-      for (int j = 0; j < nst && ok; ++j) {
-        const int s = j % kWtRing;
-        if (j >= kWtRing)
-          ok = mbar_wait(raw_empty(s), (uint32_t)((j / kWtRing - 1) & 1), &s_abort, 31);
-        if (!ok) break;
-        const uint32_t dst = smem_base + s * C::kStageBytes;
-        const int k0 = (st_begin + j) * kWtBK;
-        mbar_arrive_expect_tx(raw_full(s), C::kStageBytes);
-        tma_load_2d(dst, &map_w, w_left, wrow0 + k0, raw_full(s));
-        tma_load_2d(dst + kWtWBytes / 2, &map_w, w_right, wrow0 + k0, raw_full(s));
-        tma_load_2d(dst + kWtWBytes, &map_x, k0, m0, raw_full(s));
-        tma_load_2d(dst + kWtWBytes + NT * 128, &map_x, k0 + 64, m0, raw_full(s));
+      for (int j = kWtRing; j < nst && ok; ++j) {
+        ok = mbar_wait(raw_empty(j % kWtRing), (uint32_t)((j / kWtRing - 1) & 1), &s_abort, 31);
+        if (ok) load_stage(j);
       }
     }
   } else if (warp == kWtIssueWarp) {
@@ -283,7 +292,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ conversion warps
     const int g = lane >> 2, t = lane & 3;
-    const int q = warp & 3, r = warp >> 2;
+    // Warp (q, h, par): TMEM lane quarter q, steps 4 h .. 4 h + 3 of the stages of parity par
+    // (one set-up of the group's scales and zeros serves four steps; the chains of consecutive
+    // stages run on different warps and overlap).  In the epilogue the same warp is (q, r).
+    const int q = warp & 3, h = (warp >> 2) & 1, par = warp >> 3, r = warp >> 2;
     const uint32_t lane_q = (uint32_t)(q * 32) << 16;
     // raw tile as TMA leaves it: two boxes of [128 rows x 64 B] (64-byte swizzle): row k of box
     // q / 2 at k * 64, 16-byte chunk c at position c ^ ((k / 2) % 4).
@@ -301,20 +313,17 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint4* sp =
         reinterpret_cast<const uint4*>(p.scales + (size_t)(grp0 + st_begin) * p.N) + conv_word;
     const size_t spitch = (size_t)p.N / 8;
-    // scale / zero rows are fetched two stages ahead (registers) and six ahead (L2)
-    uint32_t zw_n = 0, zw_n2 = 0;
-    uint4 sv_n = make_uint4(0, 0, 0, 0), sv_n2 = sv_n;
-    if (nst > 0) {
-      zw_n = __ldg(zp);
-      sv_n = __ldg(sp);
-    }
-    if (nst > 1) {
-      zw_n2 = __ldg(zp + words);
-      sv_n2 = __ldg(sp + spitch);
+    // scale / zero rows of this warp's next stage (two stages on) are fetched while it converts
+    // the current one; rows further on are pulled into L2
+    uint32_t zw_n = 0;
+    uint4 sv_n = make_uint4(0, 0, 0, 0);
+    if (par < nst) {
+      zw_n = __ldg(zp + (size_t)par * words);
+      sv_n = __ldg(sp + (size_t)par * spitch);
     }
 
     bool ok = true;
-    for (int j = 0; j < nst && ok; ++j) {
+    for (int j = par; j < nst && ok; j += 2) {
       const int s = j % kWtRing;
       const uint32_t wsm = smem_base + s * C::kStageBytes;
       // zero point and scale of this lane's eight columns for the group (= stage):
@@ -324,12 +333,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       {
         const uint32_t zw = zw_n;
         const uint4 sc = sv_n;
-        zw_n = zw_n2;
-        sv_n = sv_n2;
         if (j + 2 < nst) {
-          zw_n2 = __ldg(zp + (size_t)(j + 2) * words);
-          sv_n2 = __ldg(sp + (size_t)(j + 2) * spitch);
-          if (t == 0) {
+          zw_n = __ldg(zp + (size_t)(j + 2) * words);
+          sv_n = __ldg(sp + (size_t)(j + 2) * spitch);
+          if (t == 0 && h == 0) {
             const int jp = min(j + 6, nst - 1);
             asm volatile("prefetch.global.L2 [%0];" ::"l"(zp + (size_t)jp * words));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + (size_t)jp * spitch));
@@ -356,44 +363,51 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       ok = mbar_wait(raw_full(s), (uint32_t)((j / kWtRing) & 1), &s_abort, 34);
       if (!ok) break;
-      // the MMAs of stage j - 2 must have read this half of the A ring
-      if (j >= 2) ok = mbar_wait(a_empty(j & 1), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 35);
-      if (!ok) break;
-      tc_fence_after();
-      // both steps' packed words first: the loads must not queue up behind the tcgen05.st of
-      // the first step
-      uint32_t w[2][4];
+      // all four steps' packed words first: the loads must not queue up behind tcgen05.st
+      uint32_t w[4][4];
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const uint32_t rowA = wsm + (16 * (2 * r + e)) * 64;
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t rowA = wsm + (16 * (4 * h + e)) * 64;
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) w[e][rr] = wt_lds32(rowA + off[rr]);
       }
+      // the MMAs of stage j - 2 must have read this half of the A ring
+      if (j >= 2) ok = mbar_wait(a_empty(par), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 35);
+      if (!ok) break;
+      tc_fence_after();
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int step = 2 * r + e;
-        const uint32_t u0 = prmt(w[e][0], w[e][1], 0x5410), v0 = prmt(w[e][0], w[e][1], 0x7632);
-        const uint32_t u1 = prmt(w[e][2], w[e][3], 0x5410), v1 = prmt(w[e][2], w[e][3], 0x7632);
-        const uint32_t u0h = u0 >> 8, v0h = v0 >> 8, u1h = u1 >> 8, v1h = v1 >> 8;
+      for (int sp2 = 0; sp2 < 2; ++sp2) {
+        // fragments of two steps: frag[hq][4 * (2 e + tile) + k] -- the two tiles of a step and
+        // two consecutive steps are adjacent column groups of the A ring, so one x4 store per
+        // half-quarter writes all four
+        uint32_t frag[2][16];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t mask = (i & 1) ? 0x00F000F0u : 0x000F000Fu;
-          const uint32_t su0 = (i & 2) ? u0h : u0, sv0 = (i & 2) ? v0h : v0;
-          const uint32_t su1 = (i & 2) ? u1h : u1, sv1 = (i & 2) ? v1h : v1;
-          // (col 2i: k 4t..4t+1 | 4t+2..4t+3), (col 2i+1: same); (q - z) exact, then the scale
-          const uint32_t r0 = as_u32(__hmul2(
-              __hsub2(as_half2(lop3_and_or(su0, mask, 0x64006400u)), zu[i]), su[i]));
-          const uint32_t r1 = as_u32(__hmul2(
-              __hsub2(as_half2(lop3_and_or(su1, mask, 0x64006400u)), zu[i]), su[i]));
-          const uint32_t r2 = as_u32(__hmul2(
-              __hsub2(as_half2(lop3_and_or(sv0, mask, 0x64006400u)), zv[i]), sv[i]));
-          const uint32_t r3 = as_u32(__hmul2(
-              __hsub2(as_half2(lop3_and_or(sv1, mask, 0x64006400u)), zv[i]), sv[i]));
-          // half-quarter i & 1 of this warp's lanes, weight tile i >> 1
-          wt_tmem_st(tmem + lane_q + ((uint32_t)((i & 1) * 16) << 16) + kWtColA +
-                         ((j & 1) * 8 + step) * 16 + (i >> 1) * 8,
-                     r0, r1, r2, r3);
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t* ww = w[2 * sp2 + e];
+          const uint32_t u0 = prmt(ww[0], ww[1], 0x5410), v0 = prmt(ww[0], ww[1], 0x7632);
+          const uint32_t u1 = prmt(ww[2], ww[3], 0x5410), v1 = prmt(ww[2], ww[3], 0x7632);
+          const uint32_t u0h = u0 >> 8, v0h = v0 >> 8, u1h = u1 >> 8, v1h = v1 >> 8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t mask = (i & 1) ? 0x00F000F0u : 0x000F000Fu;
+            const uint32_t su0 = (i & 2) ? u0h : u0, sv0 = (i & 2) ? v0h : v0;
+            const uint32_t su1 = (i & 2) ? u1h : u1, sv1 = (i & 2) ? v1h : v1;
+            // (col 2i: k 4t..4t+1 | 4t+2..4t+3), (col 2i+1: same); (q - z) exact, then the scale
+            const int c = 4 * (2 * e + (i >> 1));
+            frag[i & 1][c] = as_u32(__hmul2(
+                __hsub2(as_half2(lop3_and_or(su0, mask, 0x64006400u)), zu[i]), su[i]));
+            frag[i & 1][c + 1] = as_u32(__hmul2(
+                __hsub2(as_half2(lop3_and_or(su1, mask, 0x64006400u)), zu[i]), su[i]));
+            frag[i & 1][c + 2] = as_u32(__hmul2(
+                __hsub2(as_half2(lop3_and_or(sv0, mask, 0x64006400u)), zv[i]), sv[i]));
+            frag[i & 1][c + 3] = as_u32(__hmul2(
+                __hsub2(as_half2(lop3_and_or(sv1, mask, 0x64006400u)), zv[i]), sv[i]));
+          }
         }
+        // half-quarter hq of this warp's lanes; steps 4 h + 2 sp2, + 1; both tiles
+        const uint32_t a_slot = tmem + lane_q + kWtColA + (par * 8 + 4 * h + 2 * sp2) * 16;
+        wt_tmem_st_x4(a_slot, frag[0]);
+        wt_tmem_st_x4(a_slot + (16u << 16), frag[1]);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
@@ -401,7 +415,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // arrival per warp (hundreds of arrivals on one shared-memory word would serialise)
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(a_full(j & 1));
+        mbar_arrive(a_full(par));
         mbar_arrive(raw_empty(s));
       }
     }
@@ -438,7 +452,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // ---- reduction over the cluster ranks through distributed shared memory ----
   tc_fence_before();
   __syncthreads();
-  cluster.sync();
+  if (S > 1) cluster.sync();  // every rank's partial tile is in its shared memory
   if (!s_abort) {
     if (MODE == 0) {
       constexpr int kUnits = kWtBN / 8;
@@ -502,7 +516,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   }
-  cluster.sync();
+  if (S > 1) cluster.sync();  // peers are done reading this CTA's shared memory
 
   // ---- teardown ----
   tc_fence_before();
