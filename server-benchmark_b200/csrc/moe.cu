@@ -43,7 +43,9 @@ __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(
 
 constexpr int kTopkWarps = 4;
 
-template <typename T>
+// NV = entries per lane (E <= 32 NV): the selection loops run over NV, not over the 32 that the
+// largest supported expert count needs.
+template <typename T, int NV>
 __global__ void __launch_bounds__(kTopkWarps * 32)
 topk_softmax_kernel(const T* __restrict__ gating, int tokens, int E, int topk, int renorm,
                     float* __restrict__ out_w, int32_t* __restrict__ out_ids,
@@ -53,20 +55,20 @@ topk_softmax_kernel(const T* __restrict__ gating, int tokens, int E, int topk, i
   if (token >= tokens) return;
   const T* row = gating + (size_t)token * E;
   const float kNegInf = -__int_as_float(0x7f800000);
-  float v[32];
+  float v[NV];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int e = lane + 32 * i;
     v[i] = e < E ? to_f32<T>(row[e]) : kNegInf;
   }
   float mx = kNegInf;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+  for (int i = 0; i < NV; ++i) mx = fmaxf(mx, v[i]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) sum += (lane + 32 * i < E) ? __expf(v[i] - mx) : 0.f;
+  for (int i = 0; i < NV; ++i) sum += (lane + 32 * i < E) ? __expf(v[i] - mx) : 0.f;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   const float inv = 1.f / sum;
@@ -78,7 +80,7 @@ topk_softmax_kernel(const T* __restrict__ gating, int tokens, int E, int topk, i
     float bv = kNegInf;
     int bi = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int e = lane + 32 * i;
       // ascending e: a strict comparison keeps the lower id on ties
       if (e < E && !((taken >> i) & 1u) && (bi == 0x7fffffff || v[i] > bv)) {
@@ -156,13 +158,30 @@ moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
     }
   }
   __syncthreads();
-  if (tid == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) {
+  // exclusive prefix of the padded counts: thread t owns experts [t * per, (t + 1) * per),
+  // warp shuffles scan the per-thread sums, the first warp scans the eight warp sums
+  {
+    const int per = (E + kAlignThreads - 1) / kAlignThreads;
+    const int e0 = tid * per, e1 = min(E, e0 + per);
+    int mine_sum = 0;
+    for (int e = e0; e < e1; ++e) mine_sum += ((total[e] + block - 1) / block) * block;
+    int incl = mine_sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += v;
+    }
+    __shared__ int s_warp_sum[kAlignThreads / 32];
+    if (lane == 31) s_warp_sum[warp] = incl;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += s_warp_sum[w];
+    int run = base + incl - mine_sum;
+    for (int e = e0; e < e1; ++e) {
       offs[e] = run;
       run += ((total[e] + block - 1) / block) * block;
     }
-    offs[E] = run;
+    if (tid == kAlignThreads - 1) offs[E] = base + incl;
   }
   __syncthreads();
   const int post = offs[E];
@@ -468,18 +487,40 @@ int launch_clustered(void (*kernel)(const P), const P& p, dim3 grid, int S, cuda
 
 }  // namespace
 
+template <typename T, int NV>
+void launch_topk_nv(const void* gating, int T_, int E, int topk, int renormalize,
+                    float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices,
+                    cudaStream_t stream) {
+  const int grid = (T_ + kTopkWarps - 1) / kTopkWarps;
+  topk_softmax_kernel<T, NV><<<grid, kTopkWarps * 32, 0, stream>>>(
+      static_cast<const T*>(gating), T_, E, topk, renormalize, topk_weights, topk_ids,
+      token_expert_indices);
+}
+
+template <typename T>
+void launch_topk_t(const void* gating, int T_, int E, int topk, int renormalize,
+                   float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices,
+                   cudaStream_t stream) {
+  if (E <= 128)
+    launch_topk_nv<T, 4>(gating, T_, E, topk, renormalize, topk_weights, topk_ids,
+                         token_expert_indices, stream);
+  else if (E <= 256)
+    launch_topk_nv<T, 8>(gating, T_, E, topk, renormalize, topk_weights, topk_ids,
+                         token_expert_indices, stream);
+  else
+    launch_topk_nv<T, 32>(gating, T_, E, topk, renormalize, topk_weights, topk_ids,
+                          token_expert_indices, stream);
+}
+
 int launch_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                         int renormalize, float* topk_weights, int32_t* topk_ids,
                         int32_t* token_expert_indices, cudaStream_t stream) {
-  const int grid = (T + kTopkWarps - 1) / kTopkWarps;
   if (gating_dtype == 0)
-    topk_softmax_kernel<float><<<grid, kTopkWarps * 32, 0, stream>>>(
-        static_cast<const float*>(gating), T, E, topk, renormalize, topk_weights, topk_ids,
-        token_expert_indices);
+    launch_topk_t<float>(gating, T, E, topk, renormalize, topk_weights, topk_ids,
+                         token_expert_indices, stream);
   else
-    topk_softmax_kernel<__half><<<grid, kTopkWarps * 32, 0, stream>>>(
-        static_cast<const __half*>(gating), T, E, topk, renormalize, topk_weights, topk_ids,
-        token_expert_indices);
+    launch_topk_t<__half>(gating, T, E, topk, renormalize, topk_weights, topk_ids,
+                          token_expert_indices, stream);
   return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
 }
 
