@@ -231,7 +231,6 @@ moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
 
 // ------------------------------------------------------------------------------- grouped GEMMs
 
-constexpr int kMoeMT = 2;          // 16-row blocks
 constexpr bool kMoeExact = false;  // conversion used by the expert GEMMs (see stream_core.cuh)
 
 struct Gemm1Params {
@@ -246,8 +245,10 @@ struct Gemm1Params {
   int numel, topk, H, I, group;
 };
 
+// MT = token tiles of 8 per row block: 1 (8-row blocks, decode-size batches: almost every expert
+// that is hit sees one or two tokens) or 2 (16-row blocks).
+template <int MT>
 __global__ void __launch_bounds__(kThreads, 2) moe_gemm1_kernel(const Gemm1Params p) {
-  constexpr int MT = kMoeMT;
   extern __shared__ __align__(1024) uint8_t smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
@@ -349,8 +350,8 @@ struct Gemm2Params {
   int numel, H, I, group;
 };
 
+template <int MT>
 __global__ void __launch_bounds__(kThreads, 2) moe_gemm2_kernel(const Gemm2Params p) {
-  constexpr int MT = kMoeMT;
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int s_fid[8 * MT];
   cg::cluster_group cluster = cg::this_cluster();
@@ -464,8 +465,8 @@ int pick_cluster(int tiles, int KT) {
 }
 
 template <typename P>
-int launch_clustered(void (*kernel)(const P), const P& p, dim3 grid, int S, cudaStream_t stream) {
-  constexpr int smem = Cfg<kMoeMT>::kSmemBytes;
+int launch_clustered(void (*kernel)(const P), const P& p, dim3 grid, int S, int smem,
+                     cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -544,22 +545,24 @@ int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H,
 }
 
 // Row block of the permutation: 128 (tcgen05 grouped GEMMs) once an expert sees about 32 rows
-// or more on average and the shapes fit that kernel's tiles, otherwise 16 (streaming kernels).
+// or more on average and the shapes fit that kernel's tiles; 8 for decode-size batches (at most
+// two rows per expert on average: one 8-token tile streams a third faster than two); else 16.
 int moe_block_size(int T, int topk, int E, int H, int I, int group) {
-  const bool many_rows = (long long)T * topk >= 32LL * E;
-  return many_rows && moe_tc_supported(H, I, group) ? 128 : 8 * kMoeMT;
+  const long long pairs = (long long)T * topk;
+  if (pairs >= 32LL * E && moe_tc_supported(H, I, group)) return 128;
+  return pairs <= 2LL * E ? 8 : 16;
 }
 
 bool moe_supported(int H, int I, int group, int block) {
   if (block == 128) return moe_tc_supported(H, I, group);
   // gate/up halves start on 16-byte boundaries (I % 32), stages are 128 rows of K
-  return block == 8 * kMoeMT && H % kBK == 0 && I % kBK == 0 && I % 32 == 0 && H % 32 == 0 &&
+  return (block == 8 || block == 16) && H % kBK == 0 && I % kBK == 0 && I % 32 == 0 && H % 32 == 0 &&
          (group == 128 || group == 64 || group == 32);
 }
 
 size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   if (T <= 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0) return 0;
-  const int block = 8 * kMoeMT;
+  const int block = 16;  // the larger of the two streaming block sizes bounds the row count
   const int64_t cap = awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block);
   const int64_t rows = (cap + block - 1) / block * block;
   const size_t small = align_up((size_t)rows * I * sizeof(__half), 256) +
@@ -569,6 +572,41 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
     return big > small ? big : small;
   }
   return small;
+}
+
+template <int MT>
+int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel, int nblk,
+                     cudaStream_t stream) {
+  constexpr int smem = Cfg<MT>::kSmemBytes;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  if (!attr_done[dev]) {
+    if (cudaFuncSetAttribute(moe_gemm1_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess ||
+        cudaFuncSetAttribute(moe_gemm2_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+    attr_done[dev] = true;
+  }
+  {
+    Gemm1Params p{a.x, a.w13_q, a.w13_s, a.w13_z, a.sorted_ids, a.expert_ids, a.num_post_pad,
+                  act, numel, a.topk, a.H, a.I, a.group};
+    const int slabs = (a.I + 127) / 128;
+    const int S = pick_cluster(slabs * nblk, a.H / kBK);
+    if (int rc = launch_clustered(moe_gemm1_kernel<MT>, p, dim3(S, slabs, nblk), S, smem, stream))
+      return rc;
+  }
+  {
+    Gemm2Params p{act, a.w2_q, a.w2_s, a.w2_z, a.topk_weights, a.sorted_ids, a.expert_ids,
+                  a.num_post_pad, pair_out, numel, a.H, a.I, a.group};
+    const int slabs = (a.H + kBN - 1) / kBN;
+    const int S = pick_cluster(slabs * nblk, a.I / kBK);
+    if (int rc = launch_clustered(moe_gemm2_kernel<MT>, p, dim3(S, slabs, nblk), S, smem, stream))
+      return rc;
+  }
+  return AWQ_B200_OK;
 }
 
 int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes,
@@ -583,38 +621,14 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
   __half* pair_out = reinterpret_cast<__half*>(static_cast<uint8_t*>(workspace) +
                                                align_up((size_t)rows * a.I * sizeof(__half), 256));
 
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
-  if (!attr_done[dev]) {
-    constexpr int smem = Cfg<kMoeMT>::kSmemBytes;
-    if (cudaFuncSetAttribute(moe_gemm1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess ||
-        cudaFuncSetAttribute(moe_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess)
-      return AWQ_B200_ERR_LAUNCH;
-    attr_done[dev] = true;
-  }
   if (a.expert_parallel) {
     // pairs routed to experts of other ranks are never written: they must read as zero
     if (cudaMemsetAsync(pair_out, 0, (size_t)numel * a.H * sizeof(__half), stream) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
   }
-  {
-    Gemm1Params p{a.x, a.w13_q, a.w13_s, a.w13_z, a.sorted_ids, a.expert_ids, a.num_post_pad,
-                  act, numel, a.topk, a.H, a.I, a.group};
-    const int slabs = (a.I + 127) / 128;
-    const int S = pick_cluster(slabs * nblk, a.H / kBK);
-    if (int rc = launch_clustered(moe_gemm1_kernel, p, dim3(S, slabs, nblk), S, stream)) return rc;
-  }
-  {
-    Gemm2Params p{act, a.w2_q, a.w2_s, a.w2_z, a.topk_weights, a.sorted_ids, a.expert_ids,
-                  a.num_post_pad, pair_out, numel, a.H, a.I, a.group};
-    const int slabs = (a.H + kBN - 1) / kBN;
-    const int S = pick_cluster(slabs * nblk, a.I / kBK);
-    if (int rc = launch_clustered(moe_gemm2_kernel, p, dim3(S, slabs, nblk), S, stream)) return rc;
-  }
+  if (int rc = a.block == 8 ? launch_moe_gemms<1>(a, act, pair_out, numel, nblk, stream)
+                            : launch_moe_gemms<2>(a, act, pair_out, numel, nblk, stream))
+    return rc;
   {
     const long long work = (long long)a.T * (a.H / 8);
     moe_sum_kernel<<<(unsigned)((work + 255) / 256), 256, 0, stream>>>(pair_out, a.out, a.T,
