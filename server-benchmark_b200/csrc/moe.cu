@@ -545,12 +545,14 @@ int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H,
 }
 
 // Row block of the permutation: 128 (tcgen05 grouped GEMMs) once an expert sees about 32 rows
-// or more on average and the shapes fit that kernel's tiles; 8 for decode-size batches (at most
-// two rows per expert on average: one 8-token tile streams a third faster than two); else 16.
+// or more on average and the shapes fit that kernel's tiles; 8 up to eight rows per expert on
+// average (one 8-token tile streams a third faster than two, which outweighs the experts that
+// need a second block up to there: measured crossover between T = 128 and 192 at 128 experts,
+// top-8); else 16.
 int moe_block_size(int T, int topk, int E, int H, int I, int group) {
   const long long pairs = (long long)T * topk;
   if (pairs >= 32LL * E && moe_tc_supported(H, I, group)) return 128;
-  return pairs <= 2LL * E ? 8 : 16;
+  return pairs <= 8LL * E ? 8 : 16;
 }
 
 bool moe_supported(int H, int I, int group, int block) {
