@@ -47,7 +47,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel, as a ratio to
 # the launch's algorithmic bytes, from the ncu capture summarised in
 # profiles/gemm_stream_M16_K8192_N29568.md (capture of a smaller case, scaled by bytes)
-NCU_TRAFFIC_RATIO = 1.051
+NCU_TRAFFIC_RATIO = 1.028
 E2E_DEPTH = 3  # steps in flight in the end-to-end leg
 
 
