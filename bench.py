@@ -15,8 +15,8 @@ value   device-resident: the step is captured once in a CUDA graph and replayed;
         CUDA events on the launching stream between barriers, max over ranks.
 e2e     the same step through the layer API (AWQLinearMethod.apply) with the activations in
         pinned host memory: host->device copy, four kernels, device->host copy of the outputs,
-        every step; weights stay resident in HBM as they do while serving.  Three steps are in
-        flight on three streams (copies of one step overlap kernels of another).
+        every step; weights stay resident in HBM as they do while serving.  Four steps are in
+        flight on four streams (copies of one step overlap kernels of another).
 N > 1   replicas (the TP=1 scaling mode of the harness): every rank runs the same step on its
         own GPU, value is the sum; reported as weak scaling.  The tensor-parallel variant
         (column/row shards + NCCL all-reduce of the row-parallel outputs) is timed as well and
@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0
 # the launch's algorithmic bytes, from the ncu capture summarised in
 # profiles/gemm_stream_M16_K8192_N29568.md (capture of a smaller case, scaled by bytes)
 NCU_TRAFFIC_RATIO = 1.028
-E2E_DEPTH = 3  # steps in flight in the end-to-end leg
+E2E_DEPTH = 4  # steps in flight in the end-to-end leg (2: 0.255, 3: 0.206, 4: 0.201, 6: 0.198 ms per step)
 
 
 def shapes():
