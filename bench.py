@@ -44,9 +44,9 @@ UNIT = "TB/s"
 M_TOKENS = 16
 GROUP = 128
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel, as a ratio to
-# the launch's algorithmic bytes, from the ncu capture summarised in
-# profiles/gemm_stream_M16_K8192_N29568.md (capture of a smaller case, scaled by bytes)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the M = 16 kernel, as a ratio to the
+# launch's algorithmic bytes, from an ncu capture of a smaller case (K = 8192, N = 29568: 130.2 MB
+# of traffic for 126.6 MB); the traffic of the full-size launches is scaled by their bytes
 NCU_TRAFFIC_RATIO = 1.028
 E2E_DEPTH = 4  # steps in flight in the end-to-end leg (2: 0.255, 3: 0.206, 4: 0.201, 6: 0.198 ms per step)
 
@@ -319,7 +319,7 @@ def run_cuda(args):
         if rank == 0:
             sampler.stop()
 
-        # ---- BASELINE configs 2 and 3 (1 GPU only): shape sweep and MoE layer ----
+        # ---- benchmark configurations 2 and 3 (1 GPU only): shape sweep and MoE layer ----
         sweep = moe = None
         if world == 1 and not args.no_sweep:
             del graph
@@ -415,7 +415,7 @@ def graph_time(fns, stream, reps=3):
 
 
 def run_sweep(dev, stream):
-    """BASELINE config 2: the four 72B layer shapes x M in {1 .. 4096}, 1 GPU.  Weights are
+    """Benchmark configuration 2: the four 72B layer shapes x M in {1 .. 4096}, 1 GPU.  Weights are
     rotated over enough copies that every launch reads more than the L2 holds."""
     import torch
     import awq_b200
@@ -438,7 +438,7 @@ def run_sweep(dev, stream):
 
 
 def run_moe(dev, stream):
-    """BASELINE config 3: Qwen3-30B-A3B fused-MoE layer (router -> permutation -> expert GEMMs ->
+    """Benchmark configuration 3: Qwen3-30B-A3B fused-MoE layer (router -> permutation -> expert GEMMs ->
     sum), T in {1 .. 4096}, 1 GPU."""
     import torch
     import awq_b200
