@@ -77,8 +77,21 @@ int awq_b200_dequantize(const void* qweight, const void* scales, const void* qze
 #define AWQ_B200_KERNEL_TS 5       /* M <= 16: registers -> TMEM weights, tcgen05.mma (A in TMEM) */
 #define AWQ_B200_KERNEL_TS_EXACT 6 /* the same with the magic-number conversion */
 #define AWQ_B200_KERNEL_WT 7       /* any M: dequantised weights registers -> TMEM (A operand), x via TMA as B */
+#define AWQ_B200_KERNEL_STREAM_RP 8 /* M <= 8 streaming kernel; `qweight` is the output of awq_b200_repack_qweight */
 
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel);
+
+/*
+ * Optional load-time repack of qweight for the decode kernel (AWQ_B200_KERNEL_STREAM_RP):
+ * out int32 [K/4, N/8, 4] holds, for every quad of rows and packed word column, the four
+ * row-pair registers the in-kernel unpack otherwise builds with byte permutes -- a pure
+ * permutation of the bits of qweight, same size.  K % 4 == 0.  The AWQ layout stays the layout of
+ * every other kernel, so a caller that wants the faster decode kernel keeps both copies.
+ * Counterpart in the reference stack: the load-time repack of the Marlin path
+ * (quantization/awq_marlin.py:491-499), which this replaces for M <= 8; scales and qzeros are
+ * used as they are.
+ */
+int awq_b200_repack_qweight(const void* qweight, void* out, int K, int N, void* stream);
 
 int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const void* qzeros,
                   const void* bias, void* out, int M, int N, int K, int group, int kernel,

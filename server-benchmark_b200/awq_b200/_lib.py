@@ -22,6 +22,7 @@ KERNEL_STREAM_EXACT = 4
 KERNEL_TS = 5
 KERNEL_TS_EXACT = 6
 KERNEL_WT = 7
+KERNEL_STREAM_RP = 8
 
 # name -> (restype, argtypes); kept in step with include/awq_b200.h
 PROTOTYPES = {
@@ -30,6 +31,7 @@ PROTOTYPES = {
     "awq_b200_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                     c_void_p]),
     "awq_b200_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "awq_b200_repack_qweight": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "awq_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "awq_b200_device_status": (c_int, [POINTER(c_int)]),

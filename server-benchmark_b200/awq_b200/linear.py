@@ -7,7 +7,9 @@
 
 Difference from the reference: ``apply`` never materialises the fp16 weight matrix; one fused
 kernel family serves every token count (the reference switches to dequantize + matmul at 256
-tokens, awq.py:276-281).
+tokens, awq.py:276-281).  ``AWQConfig(repack_decode=True)`` additionally keeps a decode-layout
+copy of ``qweight`` (ops.awq_repack) that the streaming kernel reads for up to
+``REPACK_MAX_TOKENS`` tokens; it costs a second copy of the int4 weights and is off by default.
 """
 from __future__ import annotations
 
@@ -15,7 +17,9 @@ from dataclasses import dataclass
 
 import torch
 
-from . import ops
+from . import _lib, ops
+
+REPACK_MAX_TOKENS = 8  # the decode-layout kernel serves token counts up to this
 
 
 @dataclass
@@ -25,6 +29,7 @@ class AWQConfig:
     weight_bits: int = 4
     group_size: int = 128
     zero_point: bool = True
+    repack_decode: bool = False
 
     def __post_init__(self) -> None:
         if self.weight_bits != 4:
@@ -92,6 +97,11 @@ class AWQLinearMethod:
         for name in ("qweight", "qzeros", "scales"):
             p = getattr(layer, name)
             setattr(layer, name, torch.nn.Parameter(p.data.contiguous(), requires_grad=False))
+        layer.qweight_decode = None
+        k, words = layer.qweight.shape
+        if (self.quant_config.repack_decode and layer.group_size == 128 and k % 128 == 0
+                and words % 4 == 0):
+            layer.qweight_decode = ops.awq_repack(layer.qweight.data)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor,
               bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -101,5 +111,10 @@ class AWQLinearMethod:
         reshaped_x = x.reshape(-1, x.shape[-1])
         if not reshaped_x.is_contiguous():
             reshaped_x = reshaped_x.contiguous()
-        out = ops.awq_gemm(reshaped_x, qweight, scales, qzeros, pack_factor, bias=bias)
+        decode = getattr(layer, "qweight_decode", None)
+        if decode is not None and reshaped_x.shape[0] <= REPACK_MAX_TOKENS:
+            out = ops.awq_gemm(reshaped_x, decode, scales, qzeros, pack_factor, bias=bias,
+                               kernel=_lib.KERNEL_STREAM_RP)
+        else:
+            out = ops.awq_gemm(reshaped_x, qweight, scales, qzeros, pack_factor, bias=bias)
         return out.reshape(out_shape)

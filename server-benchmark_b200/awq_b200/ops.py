@@ -114,6 +114,28 @@ def awq_gemm(input: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
     return out
 
 
+def awq_repack(qweight: torch.Tensor) -> torch.Tensor:
+    """Decode-layout copy of ``qweight`` for ``awq_gemm(..., kernel=KERNEL_STREAM_RP)``.
+
+    The copy holds, for every four rows k..k+3 and packed word column c, the four 32-bit
+    words the streaming kernel otherwise builds with byte permutes: the low and the high
+    halfwords of the row pairs (k, k+1) and (k+2, k+3).  It is returned with the shape of
+    ``qweight`` ([K, N/8] int32; memory order [K/4, N/8, 4]) so that it can be passed where
+    ``qweight`` goes; no other kernel understands it.  Load-time counterpart of the Marlin
+    repack in vllm/model_executor/layers/quantization/awq_marlin.py:491-499.
+    """
+    _require(qweight, "qweight", torch.int32, 2)
+    k, words = qweight.shape
+    if k % 4:
+        raise ValueError("K must be a multiple of 4")
+    out = torch.empty_like(qweight)
+    if qweight.numel():
+        rc = _lib.load().awq_b200_repack_qweight(qweight.data_ptr(), out.data_ptr(), k,
+                                                 words * 8, _stream())
+        _lib.check("awq_b200_repack_qweight", rc)
+    return out
+
+
 # ------------------------------------------------------------------------------- MoE
 
 

@@ -85,6 +85,16 @@ int awq_b200_dequantize(const void* qweight, const void* scales, const void* qze
                                 N, group, static_cast<cudaStream_t>(stream));
 }
 
+int awq_b200_repack_qweight(const void* qweight, void* out, int K, int N, void* stream) {
+  if (!qweight || !out) return AWQ_B200_ERR_NULL;
+  if (K <= 0 || N <= 0 || N % awq::kPack != 0 || K % 4 != 0) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(qweight) || !aligned16(out)) return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  return awq::launch_repack_qweight(static_cast<const uint32_t*>(qweight),
+                                    static_cast<uint32_t*>(out), K, N,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel) {
   if (M <= 0 || check_awq_shape(N, K, group) != AWQ_B200_OK) return 0;
   if (kernel == AWQ_B200_KERNEL_AUTO) kernel = pick_gemm_kernel(M, N, K, group);
@@ -127,6 +137,9 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
       if (!awq::gemm_ts_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
       return awq::launch_gemm_ts(xh, qw, sc, qz, bh, oh, M, N, K, group,
                                  kernel == AWQ_B200_KERNEL_TS_EXACT, st);
+    case AWQ_B200_KERNEL_STREAM_RP:
+      if (!awq::gemm_stream_rp_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+      return awq::launch_gemm_stream_rp(xh, qw, sc, qz, bh, oh, M, N, K, group, st);
     case AWQ_B200_KERNEL_WT:
       if (!awq::gemm_wt_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
       return awq::launch_gemm_wt(xh, qw, sc, qz, bh, oh, M, N, K, group, st);

@@ -121,6 +121,12 @@ int launch_tc_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t*
                       const int32_t* num_post_pad, __half* out, int numel, int K, int N, int group,
                       int half_cols, int nblk, cudaStream_t stream);
 
+bool gemm_stream_rp_supported(int M, int N, int K, int group);
+int launch_gemm_stream_rp(const __half* x, const uint32_t* qweight_rp, const __half* scales,
+                          const uint32_t* qzeros, const __half* bias, __half* out, int M, int N,
+                          int K, int group, cudaStream_t stream);
+int launch_repack_qweight(const uint32_t* qweight, uint32_t* out, int K, int N,
+                          cudaStream_t stream);
 bool gemm_ts_supported(int M, int N, int K, int group);
 int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scales,
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,

@@ -129,4 +129,33 @@ int launch_gemm_generic(const __half* x, const uint32_t* qweight, const __half* 
   return AWQ_B200_OK;
 }
 
+// Load-time repack for the decode kernel (stream_core.cuh, RP): for every row quad and word
+// column the four row-pair registers the unpack needs, as one 16-byte unit:
+//   out[(kq * words + c) * 4 + {0, 1, 2, 3}] = { lo16(w0) | lo16(w1) << 16, hi16(w0) | hi16(w1) << 16,
+//                                               lo16(w2) | lo16(w3) << 16, hi16(w2) | hi16(w3) << 16 }
+// with w_r = qweight[(4 kq + r) * words + c].  Same size as qweight; a pure permutation of bits.
+namespace {
+__global__ void __launch_bounds__(256)
+repack_kernel(const uint32_t* __restrict__ qweight, uint4* __restrict__ out, int quads, int words) {
+  const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= (long long)quads * words) return;
+  const int kq = (int)(idx / words), c = (int)(idx % words);
+  const uint32_t* src = qweight + (size_t)(4 * kq) * words + c;
+  const uint32_t w0 = __ldg(src), w1 = __ldg(src + words), w2 = __ldg(src + 2 * (size_t)words),
+                 w3 = __ldg(src + 3 * (size_t)words);
+  out[idx] = make_uint4(prmt(w0, w1, 0x5410), prmt(w0, w1, 0x7632), prmt(w2, w3, 0x5410),
+                        prmt(w2, w3, 0x7632));
+}
+}  // namespace
+
+int launch_repack_qweight(const uint32_t* qweight, uint32_t* out, int K, int N,
+                          cudaStream_t stream) {
+  const int words = N / kPack, quads = K / 4;
+  const long long total = (long long)quads * words;
+  if (total == 0) return AWQ_B200_OK;
+  repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+      qweight, reinterpret_cast<uint4*>(out), quads, words);
+  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
 }  // namespace awq

@@ -40,7 +40,7 @@ constexpr int min_blocks(int MT, int WG) {
   return WG == 1 ? (MT == 1 ? AWQ_STREAM_BLOCKS_MT1 : (MT == 2 ? 4 : 2)) : (MT == 1 && WG <= 3 ? 2 : 1);
 }
 
-template <int MT, bool EXACT, int GROUP, int WG>
+template <int MT, bool EXACT, int GROUP, int WG, bool RP>
 __global__ void __launch_bounds__(kGroupThreads * WG, min_blocks(MT, WG))
 gemm_stream_kernel(const StreamParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -61,10 +61,18 @@ gemm_stream_kernel(const StreamParams p) {
 
   TileSrc<MT> src;
   {
-    const int wc = word0 + (tid & 7) * 4;
-    src.wvalid = wc < words;
-    src.wsrc = p.qweight + (src.wvalid ? wc : 0);
-    src.wrow_words = (size_t)words;
+    if (RP) {
+      // repacked layout [K/4][N/8][4]: this thread copies the unit of word column tid % 32
+      const int wc = word0 + (tid & 31);
+      src.wvalid = wc < words;
+      src.wsrc = p.qweight + (size_t)(src.wvalid ? wc : 0) * 4;
+      src.wrow_words = (size_t)words * 4;
+    } else {
+      const int wc = word0 + (tid & 7) * 4;
+      src.wvalid = wc < words;
+      src.wsrc = p.qweight + (src.wvalid ? wc : 0);
+      src.wrow_words = (size_t)words;
+    }
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
       const int row = (tid >> 4) + 8 * j;
@@ -80,7 +88,7 @@ gemm_stream_kernel(const StreamParams p) {
   }
 
   float tot[MT][4][4];
-  mainloop<MT, EXACT, GROUP>(src, smem_u32(smem) + wg * kRing, tid, wg, st_begin,
+  mainloop<MT, EXACT, GROUP, RP>(src, smem_u32(smem) + wg * kRing, tid, wg, st_begin,
                              st_end - st_begin, p.group, p.K / p.group, tot);
 
   // ---- reduction over warp groups and cluster ranks through (distributed) shared memory ----
@@ -124,14 +132,14 @@ gemm_stream_kernel(const StreamParams p) {
   cluster.sync();  // keep this CTA's shared memory alive until every peer has read it
 }
 
-template <int MT, bool EXACT, int GROUP, int WG>
+template <int MT, bool EXACT, int GROUP, int WG, bool RP = false>
 int launch_variant(const StreamParams& p, int S, cudaStream_t stream) {
   constexpr int smem = Cfg<MT>::kSmemBytes * WG;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
-  auto kernel = gemm_stream_kernel<MT, EXACT, GROUP, WG>;
+  auto kernel = gemm_stream_kernel<MT, EXACT, GROUP, WG, RP>;
   if (!attr_done[dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
@@ -165,7 +173,7 @@ int launch_variant(const StreamParams& p, int S, cudaStream_t stream) {
 // Split of K: S cluster ranks x WG warp groups, sized so that about 3-4 warp groups are
 // resident per SM (that is what the shared-memory rings allow) without starving a group of
 // stages.
-template <int MT, bool EXACT, int GROUP>
+template <int MT, bool EXACT, int GROUP, bool RP = false>
 int launch_split(const StreamParams& p, cudaStream_t stream) {
   const int slabs = (p.N + kBN - 1) / kBN;
   const int KT = p.K / kBK;
@@ -180,9 +188,9 @@ int launch_split(const StreamParams& p, cudaStream_t stream) {
     wg = wg < 1 ? 1 : (wg > 3 ? 3 : wg);
     while (wg > 1 && KT / (S * wg) < AWQ_STREAM_MIN_STAGES) --wg;
   }
-  if (wg == 3) return launch_variant<MT, EXACT, GROUP, 3>(p, S, stream);
-  if (wg == 2) return launch_variant<MT, EXACT, GROUP, 2>(p, S, stream);
-  return launch_variant<MT, EXACT, GROUP, 1>(p, S, stream);
+  if (wg == 3) return launch_variant<MT, EXACT, GROUP, 3, RP>(p, S, stream);
+  if (wg == 2) return launch_variant<MT, EXACT, GROUP, 2, RP>(p, S, stream);
+  return launch_variant<MT, EXACT, GROUP, 1, RP>(p, S, stream);
 }
 
 template <bool EXACT, int GROUP>
@@ -219,6 +227,19 @@ bool gemm_stream_supported(int M, int N, int K, int group) {
   // a stage is 128 rows and a group must tile it in whole 16-row steps.
   return M >= 1 && M <= 32 && N % 32 == 0 && K % kBK == 0 &&
          (group == 128 || group == 64 || group == 32);
+}
+
+bool gemm_stream_rp_supported(int M, int N, int K, int group) {
+  return M >= 1 && M <= 8 && N % 32 == 0 && K % kBK == 0 && group == 128;
+}
+
+// The same kernel on weights repacked by launch_repack_qweight (M <= 8, group 128).
+int launch_gemm_stream_rp(const __half* x, const uint32_t* qweight_rp, const __half* scales,
+                          const uint32_t* qzeros, const __half* bias, __half* out, int M, int N,
+                          int K, int group, cudaStream_t stream) {
+  if (!gemm_stream_rp_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+  StreamParams p{x, qweight_rp, scales, qzeros, bias, out, M, N, K, group};
+  return launch_split<1, false, 128, true>(p, stream);
 }
 
 int launch_gemm_stream(const __half* x, const uint32_t* qweight, const __half* scales,

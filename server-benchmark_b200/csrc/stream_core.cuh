@@ -29,6 +29,12 @@
 //          before the MMA; the scale again multiplies the fp32 group sum.
 // Both accumulate every group in fp32 and apply the fp16 scale in fp32.
 //
+// RP (repacked weights, dequantize.cu::repack_kernel): the four prmt results (u, v of rows
+// k, k+1 and of rows k+2, k+3) of every (row quad, word column) are stored as one 16-byte unit,
+// [K/4][N/8][4] words.  A stage is then copied as it lies (512 contiguous bytes per row quad)
+// and a lane's four registers come from one conflict-free ld.shared.v4: the pairing prmts and
+// three of four shared-memory loads leave the loop.
+//
 // Shared-memory layout of a weight stage: row r (128 B) at r * 128, its 16-byte chunk c stored
 // at chunk position c ^ (2 * ((r / 4) % 4) + r % 2) -- conflict-free both for the 16-byte
 // cp.async writes and for the 4-byte fragment reads.  x stage: [8 MT rows][128 + 16 halves].
@@ -68,6 +74,13 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
   asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
@@ -104,7 +117,7 @@ struct TileSrc {
 // GROUP is the quantisation group size when known at compile time (128: loops fully
 // unrolled) or 0 to take it from `group` at run time (32 / 64 / 128).
 // `tid` is the thread's index inside its warp group `wg`.
-template <int MT, bool EXACT, int GROUP>
+template <int MT, bool EXACT, int GROUP, bool RP = false>
 __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_base, int tid,
                                          int wg, int st_begin, int nst, int group, int ngroups,
                                          float (&tot)[MT][4][4]) {
@@ -116,13 +129,22 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
   auto issue_stage = [&](int st, int buf) {
     const uint32_t wbase = smem_base + buf * STAGE;
     const int k0 = st * kBK;
-    const int chunk = tid & 7, rbase = tid >> 3;
-    const uint32_t* s0 = src.wsrc + (size_t)k0 * src.wrow_words;
+    if (RP) {
+      // repacked weights: row quad q of the stage = 32 word columns x 16 B, copied as it lies;
+      // this thread: 16-byte chunk of column tid % 32, quads tid / 32 + 4 i
+      const uint32_t* s0 = src.wsrc + (size_t)(k0 / 4 + (tid >> 5)) * src.wrow_words;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int row = rbase + 16 * i;
-      cp_async16(wbase + row * 128 + ((chunk ^ row_swizzle(row)) << 4), s0 + (size_t)row * src.wrow_words,
-                 src.wvalid);
+      for (int i = 0; i < 8; ++i)
+        cp_async16(wbase + (tid + 128 * i) * 16, s0 + (size_t)(4 * i) * src.wrow_words, src.wvalid);
+    } else {
+      const int chunk = tid & 7, rbase = tid >> 3;
+      const uint32_t* s0 = src.wsrc + (size_t)k0 * src.wrow_words;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = rbase + 16 * i;
+        cp_async16(wbase + row * 128 + ((chunk ^ row_swizzle(row)) << 4),
+                   s0 + (size_t)row * src.wrow_words, src.wvalid);
+      }
     }
     const uint32_t xbase = wbase + kWStageBytes;
 #pragma unroll
@@ -205,11 +227,25 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
       for (int s2 = 0; s2 < (GROUP ? GROUP / 16 : 8); ++s2) {
         if (!GROUP && s2 >= spg) break;
         const int s = gi * spg + s2;
-        const uint32_t rowA = wsm + (16 * s + 4 * t) * 128;
-        const uint32_t w0 = lds32(rowA + offA);
-        const uint32_t w1 = lds32(rowA + 128 + offB);
-        const uint32_t w2 = lds32(rowA + 2 * 128 + offA);
-        const uint32_t w3 = lds32(rowA + 3 * 128 + offB);
+        uint32_t u0, v0, u1, v1;
+        if (RP) {
+          // the row pairs were formed when the weights were repacked: one 16-byte load
+          const uint4 qd = lds128(wsm + ((4 * s + t) * 32 + 8 * warp + g) * 16);
+          u0 = qd.x;
+          v0 = qd.y;
+          u1 = qd.z;
+          v1 = qd.w;
+        } else {
+          const uint32_t rowA = wsm + (16 * s + 4 * t) * 128;
+          const uint32_t w0 = lds32(rowA + offA);
+          const uint32_t w1 = lds32(rowA + 128 + offB);
+          const uint32_t w2 = lds32(rowA + 2 * 128 + offA);
+          const uint32_t w3 = lds32(rowA + 3 * 128 + offB);
+          u0 = prmt(w0, w1, 0x5410);
+          v0 = prmt(w0, w1, 0x7632);
+          u1 = prmt(w2, w3, 0x5410);
+          v1 = prmt(w2, w3, 0x7632);
+        }
         uint32_t b0[MT], b1[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -217,8 +253,6 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
           b0[mt] = xv.x;
           b1[mt] = xv.y;
         }
-        const uint32_t u0 = prmt(w0, w1, 0x5410), v0 = prmt(w0, w1, 0x7632);
-        const uint32_t u1 = prmt(w2, w3, 0x5410), v1 = prmt(w2, w3, 0x7632);
         const uint32_t u0h = u0 >> 8, v0h = v0 >> 8, u1h = u1 >> 8, v1h = v1 >> 8;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
