@@ -4,10 +4,34 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/awq_b200.h"
 
 namespace awq {
+
+// Programmatic dependent launch.  The decode kernels are launched with the stream-serialisation
+// attribute: when the kernel before them in the stream has let its dependents go (every CTA
+// executed pdl_launch_dependents or exited), their CTAs start on whatever SMs are free, set
+// their barriers up and prefetch WEIGHTS, which no kernel writes; pdl_wait then blocks until
+// the earlier kernel has completed and its writes are visible, and only after it are
+// activations read and outputs written.  After a kernel that never lets go, or after a copy,
+// the attribute changes nothing.  AWQ_B200_NO_PDL in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+inline bool pdl_enabled() {
+  static const bool on = getenv("AWQ_B200_NO_PDL") == nullptr;
+  return on;
+}
+// Appends the attribute at attr[n]; returns the new attribute count.
+inline int add_pdl_attribute(cudaLaunchAttribute* attr, int n) {
+  if (!pdl_enabled()) return n;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  return n + 1;
+}
 
 constexpr int kPack = 8;  // int4 values per int32 word
 

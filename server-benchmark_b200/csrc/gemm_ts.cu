@@ -158,15 +158,20 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
   const int nst = st_end - st_begin;
 
-  auto load_stage = [&](int j) {  // producer thread: TMA loads of local stage j
+  // producer thread: TMA loads of local stage j, packed weights and activations
+  auto load_w = [&](int j) {
     const int s = j % kRing;
-    const uint32_t dst = smem_base + s * kTsStageBytes;
-    const int k0 = (st_begin + j) * kTsBK;
     mbar_arrive_expect_tx(raw_full(s), kTsStageBytes);
-    tma_load_2d(dst, &map_w, word0, k0, raw_full(s));
-    tma_load_2d(dst + kTsWBytes, &map_x, k0, 0, raw_full(s));
-    tma_load_2d(dst + kTsWBytes + 2048, &map_x, k0 + 64, 0, raw_full(s));
+    tma_load_2d(smem_base + s * kTsStageBytes, &map_w, word0, (st_begin + j) * kTsBK, raw_full(s));
   };
+  auto load_x = [&](int j) {
+    const int s = j % kRing;
+    const uint32_t dst = smem_base + s * kTsStageBytes + kTsWBytes;
+    const int k0 = (st_begin + j) * kTsBK;
+    tma_load_2d(dst, &map_x, k0, 0, raw_full(s));
+    tma_load_2d(dst + 2048, &map_x, k0 + 64, 0, raw_full(s));
+  };
+  pdl_launch_dependents();
   if (warp == kProducerWarp && lane == 0) {
     // this thread sets the barriers up and has the first stages in flight before anyone else
     // is through the prologue (the first TMA round trip is the longest latency of a short CTA)
@@ -187,7 +192,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
-    for (int j = 0; j < nst && j < kRing; ++j) load_stage(j);
+    // weights first: they do not depend on the kernel before this one in the stream
+    for (int j = 0; j < nst && j < kRing; ++j) load_w(j);
+    pdl_wait();
+    for (int j = 0; j < nst && j < kRing; ++j) load_x(j);
   }
   __syncwarp();
   if (warp == kProducerWarp) {
@@ -209,7 +217,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       bool ok = true;
       for (int j = kRing; j < nst && ok; ++j) {
         ok = mbar_wait(raw_empty(j % kRing), (uint32_t)((j / kRing - 1) & 1), &s_abort, 21);
-        if (ok) load_stage(j);
+        if (ok) {
+          load_w(j);
+          load_x(j);
+        }
       }
     }
   } else if (warp == kIssueWarp) {
@@ -513,6 +524,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (S > 1) cluster.sync();  // every rank's partial tile is in its shared memory
+  pdl_wait();  // long since satisfied; orders this thread's writes of `out` after the earlier kernel
   if (!s_abort) {
     constexpr int kUnits = kTsBN / 8;
     const int ubeg = (rank * kUnits) / S, uend = ((rank + 1) * kUnits) / S;
@@ -587,13 +599,13 @@ int launch_ts(const CUtensorMap& map_w, const CUtensorMap& map_x, const TsParams
   cfg.blockDim = dim3(kTsThreads, 1, 1);
   cfg.dynamicSmemBytes = kTsSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = add_pdl_attribute(attr, 1);
   if (cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, p) != cudaSuccess) {
     cudaGetLastError();
     return AWQ_B200_ERR_LAUNCH;

@@ -171,16 +171,23 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
   const int nst = st_end - st_begin;
 
-  auto load_stage = [&](int j) {  // producer thread: TMA loads of local stage j
+  // producer thread: TMA loads of local stage j, packed weights and tokens
+  auto load_w = [&](int j) {
     const int s = j % kWtRing;
     const uint32_t dst = smem_base + s * C::kStageBytes;
     const int k0 = (st_begin + j) * kWtBK;
     mbar_arrive_expect_tx(raw_full(s), C::kStageBytes);
     tma_load_2d(dst, &map_w, w_left, wrow0 + k0, raw_full(s));
     tma_load_2d(dst + kWtWBytes / 2, &map_w, w_right, wrow0 + k0, raw_full(s));
-    tma_load_2d(dst + kWtWBytes, &map_x, k0, m0, raw_full(s));
-    tma_load_2d(dst + kWtWBytes + NT * 128, &map_x, k0 + 64, m0, raw_full(s));
   };
+  auto load_x = [&](int j) {
+    const int s = j % kWtRing;
+    const uint32_t dst = smem_base + s * C::kStageBytes + kWtWBytes;
+    const int k0 = (st_begin + j) * kWtBK;
+    tma_load_2d(dst, &map_x, k0, m0, raw_full(s));
+    tma_load_2d(dst + NT * 128, &map_x, k0 + 64, m0, raw_full(s));
+  };
+  if (MODE == 0) pdl_launch_dependents();
   if (warp == kWtProducerWarp && lane == 0) {
     // this thread sets the barriers up and has the first stages in flight before anyone else
     // is through the prologue (the first TMA round trip is the longest latency of a short CTA)
@@ -198,7 +205,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     mbar_init(d_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
-    for (int j = 0; j < nst && j < kWtRing; ++j) load_stage(j);
+    // weights first: they do not depend on the kernel before this one in the stream
+    for (int j = 0; j < nst && j < kWtRing; ++j) load_w(j);
+    pdl_wait();
+    for (int j = 0; j < nst && j < kWtRing; ++j) load_x(j);
   }
   __syncwarp();
   if (warp == kWtProducerWarp) {
@@ -220,7 +230,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       bool ok = true;
       for (int j = kWtRing; j < nst && ok; ++j) {
         ok = mbar_wait(raw_empty(j % kWtRing), (uint32_t)((j / kWtRing - 1) & 1), &s_abort, 31);
-        if (ok) load_stage(j);
+        if (ok) {
+          load_w(j);
+          load_x(j);
+        }
       }
     }
   } else if (warp == kWtIssueWarp) {
@@ -453,6 +466,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (S > 1) cluster.sync();  // every rank's partial tile is in its shared memory
+  pdl_wait();  // long since satisfied; orders this thread's writes of `out` after the earlier kernel
   if (!s_abort) {
     if (MODE == 0) {
       constexpr int kUnits = kWtBN / 8;
@@ -549,13 +563,15 @@ int launch_wt_kernel(const CUtensorMap& map_w, const CUtensorMap& map_x, const W
   cfg.blockDim = dim3(kWtThreads, 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  // the grouped modes read the routing tables of the kernels before them from their first
+  // instruction on and are launched without the attribute
+  cfg.numAttrs = MODE == 0 ? add_pdl_attribute(attr, 1) : 1;
   if (cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, p) != cudaSuccess) {
     cudaGetLastError();
     return AWQ_B200_ERR_LAUNCH;

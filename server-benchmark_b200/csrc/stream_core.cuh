@@ -126,7 +126,7 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
   const int lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
-  auto issue_stage = [&](int st, int buf) {
+  auto issue_w = [&](int st, int buf) {
     const uint32_t wbase = smem_base + buf * STAGE;
     const int k0 = st * kBK;
     if (RP) {
@@ -146,7 +146,10 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
                    s0 + (size_t)row * src.wrow_words, src.wvalid);
       }
     }
-    const uint32_t xbase = wbase + kWStageBytes;
+  };
+  auto issue_x = [&](int st, int buf) {
+    const uint32_t xbase = smem_base + buf * STAGE + kWStageBytes;
+    const int k0 = st * kBK;
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
       const int row = (tid >> 4) + 8 * j, ch = tid & 15;
@@ -176,9 +179,16 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
     sc_n = __ldg(src.ssrc + (size_t)grp * src.spitch);
   }
 
+  // Prologue: the packed weights of the first stages are requested before pdl_wait (no kernel
+  // writes them), the activations after it.  All those weight copies land in the first
+  // commit group, so the first iteration waits for the whole prologue's weights.
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s)
+    if (s < nst) issue_w(st_begin + s, s);
+  pdl_wait();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < nst) issue_stage(st_begin + s, s);
+    if (s < nst) issue_x(st_begin + s, s);
     cp_async_commit();
   }
 
@@ -187,7 +197,10 @@ __device__ __forceinline__ void mainloop(const TileSrc<MT>& src, uint32_t smem_b
     group_sync(wg);
     {
       const int nx = it + STAGES - 1;
-      if (nx < nst) issue_stage(st_begin + nx, nx % STAGES);
+      if (nx < nst) {
+        issue_w(st_begin + nx, nx % STAGES);
+        issue_x(st_begin + nx, nx % STAGES);
+      }
       cp_async_commit();
     }
     const uint32_t wsm = smem_base + (it % STAGES) * STAGE;

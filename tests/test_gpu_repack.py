@@ -68,10 +68,10 @@ def test_decode_layout_gemm_vs_oracle_and_checkpoint_layout(A, m, k, n):
 def test_decode_layout_kernel_rejects_unsupported_shapes(A):
     from awq_b200 import synth
     qw, s, qz = (t.cuda() for t in synth.awq_linear_tensors(256, 256, 128, seed=1))
-    with pytest.raises(A.AwqB200Error):   # more tokens than the kernel serves
+    with pytest.raises(ValueError):   # more tokens than the kernel serves
         A.awq_gemm(synth.activations(9, 256).cuda(), qw, s, qz, 8, kernel=A.KERNEL_STREAM_RP)
     qw, s, qz = (t.cuda() for t in synth.awq_linear_tensors(256, 256, 64, seed=1))
-    with pytest.raises(A.AwqB200Error):   # group size other than 128
+    with pytest.raises(ValueError):   # group size other than 128
         A.awq_gemm(synth.activations(1, 256).cuda(), qw, s, qz, 8, kernel=A.KERNEL_STREAM_RP)
 
 
