@@ -426,14 +426,25 @@ def run_sweep(dev, stream):
         copies = max(1, -(-200_000_000 // wbytes))
         base = [a.to(dev) for a in synth.awq_linear_tensors(k, n, GROUP, seed=1)]
         sets = [base] + [[a.clone() for a in base] for _ in range(copies - 1)]
+        decode = [awq_b200.awq_repack(q[0]) for q in sets]
         for m in synth.SWEEP_M:
             x = synth.activations(m, k).to(dev)
             fns = [(lambda q=q: awq_b200.awq_gemm(x, q[0], q[1], q[2], 8)) for q in sets]
             t = graph_time(fns, stream, reps=3 if m >= 1024 else 10)
-            out.append({"shape": name, "K": k, "N": n, "M": m, "us": round(t * 1e6, 2),
-                        "weight_GBps": round(wbytes / t / 1e9, 1),
-                        "TFLOPs": round(2.0 * m * k * n / t / 1e12, 2)})
-        del sets, base
+            row = {"shape": name, "K": k, "N": n, "M": m, "us": round(t * 1e6, 2),
+                   "weight_GBps": round(wbytes / t / 1e9, 1),
+                   "TFLOPs": round(2.0 * m * k * n / t / 1e12, 2)}
+            if m <= 8:
+                # the same layer with the optional decode-layout copy of qweight (made once, at
+                # load time: AWQConfig(repack_decode=True)); "us" above is the checkpoint layout
+                fns = [(lambda q=q, r=r: awq_b200.awq_gemm(x, r, q[1], q[2], 8,
+                                                          kernel=awq_b200.KERNEL_STREAM_RP))
+                       for q, r in zip(sets, decode)]
+                tr = graph_time(fns, stream, reps=10)
+                row["us_decode_layout"] = round(tr * 1e6, 2)
+                row["weight_GBps_decode_layout"] = round(wbytes / tr / 1e9, 1)
+            out.append(row)
+        del sets, base, decode
     return out
 
 

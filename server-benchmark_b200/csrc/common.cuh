@@ -25,12 +25,30 @@ inline bool pdl_enabled() {
   static const bool on = getenv("AWQ_B200_NO_PDL") == nullptr;
   return on;
 }
+// Plain (non-cluster) launch with the attribute.  The kernel must execute pdl_wait before it
+// touches anything an earlier kernel writes or reads.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args);
 // Appends the attribute at attr[n]; returns the new attribute count.
 inline int add_pdl_attribute(cudaLaunchAttribute* attr, int n) {
   if (!pdl_enabled()) return n;
   attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[n].val.programmaticStreamSerializationAllowed = 1;
   return n + 1;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = add_pdl_attribute(attr, 0);
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 constexpr int kPack = 8;  // int4 values per int32 word

@@ -52,6 +52,8 @@ topk_softmax_kernel(const T* __restrict__ gating, int tokens, int E, int topk, i
                     int32_t* __restrict__ out_tok) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x * kTopkWarps + warp;
+  pdl_launch_dependents();
+  pdl_wait();
   if (token >= tokens) return;
   const T* row = gating + (size_t)token * E;
   const float kNegInf = -__int_as_float(0x7f800000);
@@ -134,6 +136,7 @@ moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
                  int64_t capacity, int32_t* __restrict__ expert_ids,
                  int32_t* __restrict__ num_post_pad) {
   extern __shared__ int sm[];
+  pdl_launch_dependents();
   int* total = sm;                 // [E]   histogram of all ids
   int* prior = sm + E;             // [E]   histogram of ids before this chunk
   int* offs = sm + 2 * E;          // [E+1] padded exclusive prefix
@@ -146,6 +149,7 @@ moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
   const int last = min(numel, first + per_cta * kAlignChunk);
   for (int i = tid; i < 3 * E + 1 + 8 * E; i += kAlignThreads) sm[i] = 0;
   __syncthreads();
+  pdl_wait();
   auto valid = [&](int id) {
     return id >= 0 && id < E && (expert_map == nullptr || expert_map[id] >= 0);
   };
@@ -255,10 +259,13 @@ __global__ void __launch_bounds__(kThreads, 2) moe_gemm1_kernel(const Gemm1Param
   const int S = (int)cluster.num_blocks();
   const int blk = blockIdx.z;
   const int pos0 = blk * (8 * MT);
+  pdl_launch_dependents();
+  pdl_wait();  // the routing tables come from the kernels before this one
   // uniform over the cluster: nobody reaches a cluster barrier if the block is unused
-  if (pos0 >= p.num_post_pad[0]) return;
+  // both loads in flight together (expert_ids covers every block of the grid)
+  const int post = p.num_post_pad[0];
   const int e = p.expert_ids[blk];
-  if (e < 0) return;
+  if (pos0 >= post || e < 0) return;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2;
@@ -359,9 +366,12 @@ __global__ void __launch_bounds__(kThreads, 2) moe_gemm2_kernel(const Gemm2Param
   const int S = (int)cluster.num_blocks();
   const int blk = blockIdx.z;
   const int pos0 = blk * (8 * MT);
-  if (pos0 >= p.num_post_pad[0]) return;
+  pdl_launch_dependents();
+  pdl_wait();
+  // both loads in flight together (expert_ids covers every block of the grid)
+  const int post = p.num_post_pad[0];
   const int e = p.expert_ids[blk];
-  if (e < 0) return;
+  if (pos0 >= post || e < 0) return;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2;
@@ -438,6 +448,8 @@ moe_sum_kernel(const __half* __restrict__ pair_out, __half* __restrict__ out, in
                int H) {
   const int units = H / 8;
   const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (idx >= (long long)T * units) return;
   const int t = (int)(idx / units), u = (int)(idx % units);
   float v[8];
@@ -472,13 +484,13 @@ int launch_clustered(void (*kernel)(const P), const P& p, dim3 grid, int S, int 
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = add_pdl_attribute(attr, 1);
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
     cudaGetLastError();
     return AWQ_B200_ERR_LAUNCH;
@@ -493,9 +505,9 @@ void launch_topk_nv(const void* gating, int T_, int E, int topk, int renormalize
                     float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices,
                     cudaStream_t stream) {
   const int grid = (T_ + kTopkWarps - 1) / kTopkWarps;
-  topk_softmax_kernel<T, NV><<<grid, kTopkWarps * 32, 0, stream>>>(
-      static_cast<const T*>(gating), T_, E, topk, renormalize, topk_weights, topk_ids,
-      token_expert_indices);
+  launch_pdl(topk_softmax_kernel<T, NV>, dim3(grid), dim3(kTopkWarps * 32), 0, stream,
+             static_cast<const T*>(gating), T_, E, topk, renormalize, topk_weights, topk_ids,
+             token_expert_indices);
 }
 
 template <typename T>
@@ -531,17 +543,24 @@ int launch_moe_align(const int32_t* topk_ids, int numel, int E, int block,
   const int nchunks = (numel + kAlignChunk - 1) / kAlignChunk;
   const int grid = nchunks < 1 ? 1 : (nchunks < kAlignMaxCtas ? nchunks : kAlignMaxCtas);
   const size_t smem = (size_t)(3 * E + 1 + 8 * E) * sizeof(int);  // <= 45 KB for E <= 1024
-  moe_align_kernel<<<grid, kAlignThreads, smem, stream>>>(topk_ids, numel, E, block, expert_map,
-                                                       sorted_ids, sorted_capacity, expert_ids,
-                                                       num_post_pad);
-  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+  if (launch_pdl(moe_align_kernel, dim3(grid), dim3(kAlignThreads), smem, stream, topk_ids, numel,
+                 E, block, expert_map, sorted_ids, sorted_capacity, expert_ids,
+                 num_post_pad) != cudaSuccess) {
+    cudaGetLastError();
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
 }
 
 int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H,
                    cudaStream_t stream) {
   const long long work = (long long)T * (H / 8);
-  moe_sum_kernel<<<(unsigned)((work + 255) / 256), 256, 0, stream>>>(pair_out, out, T, topk, H);
-  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+  if (launch_pdl(moe_sum_kernel, dim3((unsigned)((work + 255) / 256)), dim3(256), 0, stream,
+                 pair_out, out, T, topk, H) != cudaSuccess) {
+    cudaGetLastError();
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  return AWQ_B200_OK;
 }
 
 // Row block of the permutation: 128 (tcgen05 grouped GEMMs) once an expert sees about 32 rows
@@ -633,9 +652,11 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
     return rc;
   {
     const long long work = (long long)a.T * (a.H / 8);
-    moe_sum_kernel<<<(unsigned)((work + 255) / 256), 256, 0, stream>>>(pair_out, a.out, a.T,
-                                                                       a.topk, a.H);
-    if (cudaGetLastError() != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
+    if (launch_pdl(moe_sum_kernel, dim3((unsigned)((work + 255) / 256)), dim3(256), 0, stream,
+                   (const __half*)pair_out, a.out, a.T, a.topk, a.H) != cudaSuccess) {
+      cudaGetLastError();
+      return AWQ_B200_ERR_LAUNCH;
+    }
   }
   return AWQ_B200_OK;
 }
