@@ -172,3 +172,44 @@ def test_against_installed_vllm_kernels(A):
     y_ref = vops.awq_gemm(x, qw, s, qz, 8)
     y = A.awq_gemm(x, qw, s, qz, 8)
     assert O.rel_err(y.cpu().numpy(), y_ref.float().cpu().numpy()) < TOL
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 64])
+def test_back_to_back_layers_see_each_others_outputs(A, m):
+    """The decode kernels start before the kernel ahead of them in the stream has finished
+    (programmatic dependent launch) and prefetch weights meanwhile.  A chain in which every
+    layer reads the output of the one before, launched without any host synchronisation, must
+    give exactly what the same chain gives with a device synchronisation after every layer."""
+    from awq_b200 import synth
+    dims = [(2048, 2048), (2048, 4096), (4096, 2048), (2048, 2048)]
+    layers = [[t.cuda() for t in synth.awq_linear_tensors(k, n, 128, seed=40 + i)]
+              for i, (k, n) in enumerate(dims)]
+    x0 = (synth.activations(m, dims[0][0], seed=m) * 0.25).cuda()
+
+    def chain(sync):
+        y = x0
+        for qw, s, qz in layers:
+            y = A.awq_gemm(y, qw, s, qz, 8)
+            y = y * 0.03125  # an elementwise kernel between the layers, as a model has
+            if sync:
+                torch.cuda.synchronize()
+        return y
+
+    want = chain(True)
+    assert torch.isfinite(want.float()).all() and want.float().abs().max() > 0
+    for _ in range(10):
+        got = chain(False)
+        assert torch.equal(got, want)
+    # and straight from one linear into the next, no kernel in between
+    for _ in range(10):
+        y = x0
+        outs = []
+        for qw, s, qz in layers[:1] + layers[3:]:
+            y = A.awq_gemm(y, qw, s, qz, 8)
+            outs.append(y)
+        torch.cuda.synchronize()
+        ref = x0
+        for (qw, s, qz), o in zip(layers[:1] + layers[3:], outs):
+            ref = A.awq_gemm(ref, qw, s, qz, 8)
+            torch.cuda.synchronize()
+            assert torch.equal(ref, o)
