@@ -527,8 +527,8 @@ def run_tp(args, world, rank, dev, stream, barrier):
 def run_case(args):
     """`--case kernel:M:K:N` launches one AWQ linear of that shape `--steps` times after
     `--warmup` launches and prints its CUDA-event time: the small, bounded command the ncu
-    captures under profiles/ are taken with.  kernel: auto | stream | stream_exact | tcgen05 |
-    ts | wt | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
+    captures under profiles/ are taken with.  kernel: auto | stream | stream_exact | stream_rp
+    (decode-layout copy of qweight) | tcgen05 | ts | wt | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
     import torch
 
     import build as awq_build
@@ -559,7 +559,10 @@ def run_case(args):
             kern = {"auto": awq_b200.KERNEL_AUTO, "stream": awq_b200.KERNEL_STREAM,
                     "stream_exact": awq_b200.KERNEL_STREAM_EXACT,
                     "tcgen05": awq_b200.KERNEL_TCGEN05, "ts": awq_b200.KERNEL_TS, "wt": awq_b200.KERNEL_WT,
+                    "stream_rp": awq_b200.KERNEL_STREAM_RP,
                     "generic": awq_b200.KERNEL_GENERIC}[f[0]]
+            if f[0] == "stream_rp":
+                qw = awq_b200.awq_repack(qw)
             fn = lambda: awq_b200.awq_gemm(x, qw, s, qz, 8, kernel=kern)  # noqa: E731
         work = f"{f[0]} M={m} K={k} N={n}"
     for _ in range(args.warmup):
