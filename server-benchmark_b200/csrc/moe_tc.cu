@@ -24,19 +24,34 @@ namespace {
 constexpr int kMBM = 128;
 
 // x_perm[pos, :] = x[token(pos), :] for the rows of the used blocks; padding rows are zero.
-__global__ void __launch_bounds__(256)
+// One warp per row, eight rows per CTA; a lane keeps four 16-byte loads in flight.
+constexpr int kGatherRows = 8;
+__global__ void __launch_bounds__(32 * kGatherRows)
 moe_gather_kernel(const __half* __restrict__ x, const int32_t* __restrict__ sorted_ids,
-                  const int32_t* __restrict__ num_post_pad, __half* __restrict__ x_perm, int numel,
-                  int topk, int H) {
-  const int pos = blockIdx.x;
-  if (pos >= num_post_pad[0]) return;
-  const int fid = sorted_ids[pos];
+                  const int32_t* __restrict__ num_post_pad, __half* __restrict__ x_perm,
+                  int64_t capacity, int numel, int topk, int H) {
+  const int lane = threadIdx.x & 31;
+  const int64_t pos = (int64_t)blockIdx.x * kGatherRows + (threadIdx.x >> 5);
+  // both loads in flight together
+  const int post = num_post_pad[0];
+  const int fid = pos < capacity ? sorted_ids[pos] : numel;
+  if (pos >= post) return;
   uint4* dst = reinterpret_cast<uint4*>(x_perm + (size_t)pos * H);
+  const int units = H / 8;
   if (fid < numel) {
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(fid / topk) * H);
-    for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = __ldg(src + i);
+    int i = lane;
+    for (; i + 96 < units; i += 128) {
+      const uint4 a = __ldg(src + i), b = __ldg(src + i + 32), c = __ldg(src + i + 64),
+                  d = __ldg(src + i + 96);
+      dst[i] = a;
+      dst[i + 32] = b;
+      dst[i + 64] = c;
+      dst[i + 96] = d;
+    }
+    for (; i < units; i += 32) dst[i] = __ldg(src + i);
   } else {
-    for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = make_uint4(0, 0, 0, 0);
+    for (int i = lane; i < units; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -77,8 +92,9 @@ int launch_moe_experts_tc(const MoeArgs& a, void* workspace, size_t workspace_by
     if (cudaMemsetAsync(pair_out, 0, (size_t)numel * a.H * 2, stream) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
   }
-  moe_gather_kernel<<<(unsigned)rows, 256, 0, stream>>>(a.x, a.sorted_ids, a.num_post_pad, x_perm,
-                                                        numel, a.topk, a.H);
+  moe_gather_kernel<<<(unsigned)((rows + kGatherRows - 1) / kGatherRows), 32 * kGatherRows, 0,
+                      stream>>>(a.x, a.sorted_ids, a.num_post_pad, x_perm, a.sorted_capacity, numel,
+                                a.topk, a.H);
   if (cudaGetLastError() != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
   // group 128: dequantised weights in TMEM as the A operand (gemm_wt.cu), padding tokens cost no
   // weight work there; group 64: weights dequantised into a shared-memory B tile (gemm_tc.cu)
