@@ -251,8 +251,10 @@ struct Gemm1Params {
 
 // MT = token tiles of 8 per row block: 1 (8-row blocks, decode-size batches: almost every expert
 // that is hit sees one or two tokens) or 2 (16-row blocks).
-template <int MT>
-__global__ void __launch_bounds__(kThreads, 2) moe_gemm1_kernel(const Gemm1Params p) {
+// GROUP: the quantisation group size when it is 128 (inner loops fully unrolled), else 0 (taken
+// from the parameters at run time).
+template <int MT, int GROUP>
+__global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(const Gemm1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, 2) moe_gemm1_kernel(const Gemm1Param
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
 
   float tot[MT][4][4];
-  mainloop<MT, kMoeExact, 0>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
+  mainloop<MT, kMoeExact, GROUP>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
                               groups, tot);
 
   float* red = reinterpret_cast<float*>(smem);
@@ -357,8 +359,8 @@ struct Gemm2Params {
   int numel, H, I, group;
 };
 
-template <int MT>
-__global__ void __launch_bounds__(kThreads, 2) moe_gemm2_kernel(const Gemm2Params p) {
+template <int MT, int GROUP>
+__global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(const Gemm2Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int s_fid[8 * MT];
   cg::cluster_group cluster = cg::this_cluster();
@@ -407,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 2) moe_gemm2_kernel(const Gemm2Param
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
 
   float tot[MT][4][4];
-  mainloop<MT, kMoeExact, 0>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
+  mainloop<MT, kMoeExact, GROUP>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
                               groups, tot);
 
   float* red = reinterpret_cast<float*>(smem);
@@ -595,7 +597,7 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   return small;
 }
 
-template <int MT>
+template <int MT, int GROUP>
 int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel, int nblk,
                      cudaStream_t stream) {
   constexpr int smem = Cfg<MT>::kSmemBytes;
@@ -604,9 +606,9 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
   if (!attr_done[dev]) {
-    if (cudaFuncSetAttribute(moe_gemm1_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(moe_gemm1_kernel<MT, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem) != cudaSuccess ||
-        cudaFuncSetAttribute(moe_gemm2_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(moe_gemm2_kernel<MT, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
@@ -616,7 +618,7 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
                   act, numel, a.topk, a.H, a.I, a.group};
     const int slabs = (a.I + 127) / 128;
     const int S = pick_cluster(slabs * nblk, a.H / kBK);
-    if (int rc = launch_clustered(moe_gemm1_kernel<MT>, p, dim3(S, slabs, nblk), S, smem, stream))
+    if (int rc = launch_clustered(moe_gemm1_kernel<MT, GROUP>, p, dim3(S, slabs, nblk), S, smem, stream))
       return rc;
   }
   {
@@ -624,7 +626,7 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
                   a.num_post_pad, pair_out, numel, a.H, a.I, a.group};
     const int slabs = (a.H + kBN - 1) / kBN;
     const int S = pick_cluster(slabs * nblk, a.I / kBK);
-    if (int rc = launch_clustered(moe_gemm2_kernel<MT>, p, dim3(S, slabs, nblk), S, smem, stream))
+    if (int rc = launch_clustered(moe_gemm2_kernel<MT, GROUP>, p, dim3(S, slabs, nblk), S, smem, stream))
       return rc;
   }
   return AWQ_B200_OK;
@@ -647,9 +649,14 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
     if (cudaMemsetAsync(pair_out, 0, (size_t)numel * a.H * sizeof(__half), stream) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
   }
-  if (int rc = a.block == 8 ? launch_moe_gemms<1>(a, act, pair_out, numel, nblk, stream)
-                            : launch_moe_gemms<2>(a, act, pair_out, numel, nblk, stream))
-    return rc;
+  int rc;
+  if (a.group == 128)
+    rc = a.block == 8 ? launch_moe_gemms<1, 128>(a, act, pair_out, numel, nblk, stream)
+                      : launch_moe_gemms<2, 128>(a, act, pair_out, numel, nblk, stream);
+  else
+    rc = a.block == 8 ? launch_moe_gemms<1, 0>(a, act, pair_out, numel, nblk, stream)
+                      : launch_moe_gemms<2, 0>(a, act, pair_out, numel, nblk, stream);
+  if (rc) return rc;
   {
     const long long work = (long long)a.T * (a.H / 8);
     if (launch_pdl(moe_sum_kernel, dim3((unsigned)((work + 255) / 256)), dim3(256), 0, stream,
