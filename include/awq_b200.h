@@ -7,6 +7,13 @@
  * including scratch; the library allocates nothing, keeps no pointer after the call returns
  * and never synchronises the stream.  All work is enqueued on `stream`.
  *
+ * Most kernels are launched with CUDA's programmatic-stream-serialisation attribute: a kernel of
+ * this library that follows another one on the stream starts early, prefetches weights (which
+ * no kernel writes) and waits for the earlier kernel to complete before it reads activations or
+ * writes anything.  Stream order as the caller sees it is unchanged; the weights passed to a
+ * call must not be written by work still in flight on the same stream.  AWQ_B200_NO_PDL in the
+ * environment (read once) makes every launch a plain one.
+ *
  * Return value: AWQ_B200_OK (0) or a negative AWQ_B200_ERR_* code.  Arguments are validated on
  * the host before anything is launched; a kernel never traps.
  *
