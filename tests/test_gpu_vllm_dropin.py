@@ -52,3 +52,47 @@ def test_vllm_awq_linear_method_runs_on_our_ops(built_library):
     y = torch.ops._C.awq_gemm(synth.activations(4, k).cuda(), layer.qweight, layer.scales,
                               layer.qzeros, 8)
     assert y.shape == (4, n)
+
+
+def test_vllm_linear_method_with_decode_copy(built_library):
+    """register(repack_decode=True): vLLM's own AWQLinearMethod keeps the decode-layout copy after
+    loading and serves small batches from it."""
+    try:
+        import vllm._C  # noqa: F401
+        from vllm.model_executor.layers.quantization import awq as vllm_awq
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"vllm not usable here: {e}")
+    from awq_b200 import synth, vllm_plugin
+    saved = (vllm_awq.AWQLinearMethod.apply,
+             vllm_awq.AWQLinearMethod.process_weights_after_loading)
+    try:
+        vllm_plugin.register(repack_decode=True)
+        vllm_plugin.register(repack_decode=True)   # idempotent
+        k, n = 2048, 1536
+        qw, s, qz = synth.awq_linear_tensors(k, n, 128, seed=43)
+        try:
+            cfg = vllm_awq.AWQConfig(weight_bits=4, group_size=128, zero_point=True)
+        except TypeError:
+            cfg = vllm_awq.AWQConfig(4, 128, True)
+        method = vllm_awq.AWQLinearMethod(cfg)
+
+        class Layer(torch.nn.Module):
+            pass
+
+        layer = Layer()
+        layer.qweight = torch.nn.Parameter(qw.cuda(), requires_grad=False)
+        layer.scales = torch.nn.Parameter(s.cuda(), requires_grad=False)
+        layer.qzeros = torch.nn.Parameter(qz.cuda(), requires_grad=False)
+        method.process_weights_after_loading(layer)
+        assert layer.qweight_decode is not None
+        assert layer.qweight_decode.shape == layer.qweight.shape
+        for m in (1, 8, 9, 300):
+            x = synth.activations(m, k, seed=m).cuda()
+            y = method.apply(layer, x)
+            assert y.shape == (m, n) and y.dtype == torch.float16
+            ref = O.awq_gemm_fp32(x.cpu().numpy(), qw.numpy(), s.numpy(), qz.numpy(), 128)
+            assert O.rel_err(y.float().cpu().numpy(), ref) < 1e-2
+    finally:
+        (vllm_awq.AWQLinearMethod.apply,
+         vllm_awq.AWQLinearMethod.process_weights_after_loading) = saved
+        vllm_awq.AWQLinearMethod._awq_b200_repack = False
