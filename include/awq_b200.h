@@ -155,8 +155,11 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * once an expert sees about 32 rows or more on average.
  * Replaces fused_experts / fused_experts_impl (fused_moe/fused_moe.py:1587-1631,1664-1869)
  * and the Marlin expert path (fused_moe/experts/marlin_moe.py:225-262).
- * E is the number of stacked (local) experts.  expert_parallel != 0 says sorted_ids was built
- * with an expert_map, i.e. some (token, slot) pairs have no expert here and contribute zero.
+ * E is the number of stacked (local) experts.  `expert_parallel` is a set of flags: bit 0 says
+ * sorted_ids was built with an expert_map, i.e. some (token, slot) pairs have no expert here and
+ * contribute zero; bit 1 says w13_q and w2_q are decode-layout copies (awq_b200_repack_qweight
+ * over all E * H, respectively E * I, stacked rows), which only the weight-streaming kernels
+ * read: block 8 or 16 and group 128, anything else returns AWQ_B200_ERR_SHAPE.
  * Scratch: awq_b200_moe_workspace_bytes(T, topk, E_global, H, I) bytes, 256-byte aligned.
  * Requires H % 128 == 0, I % 128 == 0, group in {32, 64, 128}.
  */

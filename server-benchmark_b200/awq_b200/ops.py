@@ -121,17 +121,22 @@ def awq_repack(qweight: torch.Tensor) -> torch.Tensor:
     words the streaming kernel otherwise builds with byte permutes: the low and the high
     halfwords of the row pairs (k, k+1) and (k+2, k+3).  It is returned with the shape of
     ``qweight`` ([K, N/8] int32; memory order [K/4, N/8, 4]) so that it can be passed where
-    ``qweight`` goes; no other kernel understands it.  Load-time counterpart of the Marlin
+    ``qweight`` goes; no other kernel understands it.  A stacked expert tensor [E, K, N/8] is
+    repacked expert by expert (for ``fused_experts(..., w1_decode=, w2_decode=)``).  Load-time counterpart of the Marlin
     repack in vllm/model_executor/layers/quantization/awq_marlin.py:491-499.
     """
-    _require(qweight, "qweight", torch.int32, 2)
-    k, words = qweight.shape
+    _require(qweight, "qweight", torch.int32)
+    if qweight.dim() not in (2, 3):
+        raise ValueError("qweight must be [K, N/8] or stacked [E, K, N/8]")
+    k, words = qweight.shape[-2:]
     if k % 4:
         raise ValueError("K must be a multiple of 4")
     out = torch.empty_like(qweight)
     if qweight.numel():
-        rc = _lib.load().awq_b200_repack_qweight(qweight.data_ptr(), out.data_ptr(), k,
-                                                 words * 8, _stream())
+        # stacked experts: K % 4 == 0, so no row quad crosses an expert and the stack repacks
+        # as one [E * K, N/8] matrix
+        rc = _lib.load().awq_b200_repack_qweight(qweight.data_ptr(), out.data_ptr(),
+                                                 qweight.numel() // words, words * 8, _stream())
         _lib.check("awq_b200_repack_qweight", rc)
     return out
 
@@ -207,10 +212,17 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
 def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tensor,
                   topk_ids: torch.Tensor, inplace: bool = False, activation: str = "silu",
                   apply_router_weight_on_input: bool = False, global_num_experts: int = -1,
-                  expert_map: torch.Tensor | None = None, group_size: int = 128) -> torch.Tensor:
+                  expert_map: torch.Tensor | None = None, group_size: int = 128,
+                  w1_decode: torch.Tensor | None = None,
+                  w2_decode: torch.Tensor | None = None) -> torch.Tensor:
     """AWQ fused-MoE experts.  ``w1`` and ``w2`` are (qweight, scales, qzeros) triples of the
     stacked AWQ tensors: w1 = (i32 [E,H,2I/8], f16 [E,H/G,2I], i32 [E,H/G,2I/8]),
-    w2 = (i32 [E,I,H/8], f16 [E,I/G,H], i32 [E,I/G,H/8]).  Returns fp16 [T, H]."""
+    w2 = (i32 [E,I,H/8], f16 [E,I/G,H], i32 [E,I/G,H/8]).  Returns fp16 [T, H].
+
+    ``w1_decode`` / ``w2_decode`` (both or neither): ``awq_repack`` of the two stacked qweights,
+    made once at load time.  Batches small enough for the weight-streaming expert kernels
+    (``awq_b200_moe_block_size`` 8 or 16, group 128) then read those copies; larger batches
+    use ``w1`` / ``w2`` as always."""
     if activation != "silu":
         raise ValueError("only the silu activation is implemented")
     if apply_router_weight_on_input:
@@ -241,12 +253,23 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
         raise ValueError("topk_weights / topk_ids shape mismatch")
     if global_num_experts not in (-1, e) and expert_map is None:
         raise ValueError("global_num_experts differs from the stacked expert count")
+    if (w1_decode is None) != (w2_decode is None):
+        raise ValueError("w1_decode and w2_decode go together")
+    if w1_decode is not None:
+        _require(w1_decode, "w1_decode", torch.int32, 3)
+        _require(w2_decode, "w2_decode", torch.int32, 3)
+        if w1_decode.shape != w13_q.shape or w2_decode.shape != w2_q.shape:
+            raise ValueError("decode-layout copies must have the shapes of the qweights")
     out = hidden_states if inplace else torch.empty_like(hidden_states)
     if t == 0:
         return out
     lib = _lib.load()
     n_global = e if global_num_experts == -1 else global_num_experts
     block = lib.awq_b200_moe_block_size(t, topk, n_global, h, inter, g)
+    flags = int(expert_map is not None)
+    if w1_decode is not None and block in (8, 16) and g == 128:
+        w13_q, w2_q = w1_decode, w2_decode
+        flags |= 2
     sorted_ids, expert_ids, num_post = moe_align_block_size(
         topk_ids, block, n_global, expert_map, ignore_invalid_experts=True)
     need = lib.awq_b200_moe_workspace_bytes(t, topk, n_global, h, inter)
@@ -255,7 +278,7 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
         hidden_states.data_ptr(), w13_q.data_ptr(), w13_s.data_ptr(), w13_z.data_ptr(),
         w2_q.data_ptr(), w2_s.data_ptr(), w2_z.data_ptr(), topk_weights.data_ptr(),
         sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), out.data_ptr(),
-        t, topk, e, h, inter, g, block, int(expert_map is not None), sorted_ids.numel(),
+        t, topk, e, h, inter, g, block, flags, sorted_ids.numel(),
         ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
         _stream())
     _lib.check("awq_b200_moe_experts", rc)

@@ -253,7 +253,8 @@ int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, co
                  static_cast<__half*>(out),
                  T, topk, E, H, I, group, block,
                  sorted_capacity,
-                 expert_parallel};
+                 expert_parallel & 1,
+                 (expert_parallel >> 1) & 1};
   return awq::launch_moe_experts(a, workspace, workspace_bytes,
                                  static_cast<cudaStream_t>(stream));
 }
@@ -299,7 +300,8 @@ int awq_b200_moe_experts_static(const void* x, const void* w13_q, const void* w1
                  static_cast<__half*>(out),
                  T, topk, E, H, I, group, block,
                  sorted_capacity,
-                 expert_parallel};
+                 expert_parallel & 1,
+                 (expert_parallel >> 1) & 1};
   return awq::launch_moe_experts_static(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -211,6 +211,7 @@ struct MoeArgs {
   int T, topk, E, H, I, group, block;
   int64_t sorted_capacity;
   int expert_parallel;
+  int decode_layout;  // w13_q / w2_q are decode-layout copies (blocks of 8 or 16 rows only)
 };
 bool moe_supported(int H, int I, int group, int block);
 size_t moe_workspace_bytes(int T, int topk, int E, int H, int I);

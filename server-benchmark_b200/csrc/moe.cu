@@ -252,8 +252,9 @@ struct Gemm1Params {
 // MT = token tiles of 8 per row block: 1 (8-row blocks, decode-size batches: almost every expert
 // that is hit sees one or two tokens) or 2 (16-row blocks).
 // GROUP: the quantisation group size when it is 128 (inner loops fully unrolled), else 0 (taken
-// from the parameters at run time).
-template <int MT, int GROUP>
+// from the parameters at run time).  RP: the packed expert weights are the decode-layout copy
+// (launch_repack_qweight over the stacked rows; see stream_core.cuh).
+template <int MT, int GROUP, bool RP>
 __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(const Gemm1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   cg::cluster_group cluster = cg::this_cluster();
@@ -281,12 +282,22 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(co
 
   TileSrc<MT> src;
   {
-    const int c = tid & 7;
-    const int in_seg = seg0 + (c & 3) * 4;       // word inside the half
-    src.wvalid = in_seg < iw;
-    const int wc = (c < 4 ? 0 : iw) + (src.wvalid ? in_seg : 0);
-    src.wsrc = wq + wc;
-    src.wrow_words = (size_t)words;
+    if (RP) {
+      // this thread copies the 16-byte unit of word column tid % 32: 0-15 gate, 16-31 up
+      const int c = tid & 31;
+      const int in_seg = seg0 + (c & 15);
+      src.wvalid = in_seg < iw;
+      const int wc = (c < 16 ? 0 : iw) + (src.wvalid ? in_seg : 0);
+      src.wsrc = wq + (size_t)wc * 4;
+      src.wrow_words = (size_t)words * 4;
+    } else {
+      const int c = tid & 7;
+      const int in_seg = seg0 + (c & 3) * 4;       // word inside the half
+      src.wvalid = in_seg < iw;
+      const int wc = (c < 4 ? 0 : iw) + (src.wvalid ? in_seg : 0);
+      src.wsrc = wq + wc;
+      src.wrow_words = (size_t)words;
+    }
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
       const int row = (tid >> 4) + 8 * j;
@@ -308,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(co
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
 
   float tot[MT][4][4];
-  mainloop<MT, kMoeExact, GROUP>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
+  mainloop<MT, kMoeExact, GROUP, RP>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
                               groups, tot);
 
   float* red = reinterpret_cast<float*>(smem);
@@ -359,7 +370,7 @@ struct Gemm2Params {
   int numel, H, I, group;
 };
 
-template <int MT, int GROUP>
+template <int MT, int GROUP, bool RP>
 __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(const Gemm2Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int s_fid[8 * MT];
@@ -387,10 +398,17 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(co
 
   TileSrc<MT> src;
   {
-    const int wc = word0 + (tid & 7) * 4;
-    src.wvalid = wc < words;
-    src.wsrc = wq + (src.wvalid ? wc : 0);
-    src.wrow_words = (size_t)words;
+    if (RP) {
+      const int wc = word0 + (tid & 31);
+      src.wvalid = wc < words;
+      src.wsrc = wq + (size_t)(src.wvalid ? wc : 0) * 4;
+      src.wrow_words = (size_t)words * 4;
+    } else {
+      const int wc = word0 + (tid & 7) * 4;
+      src.wvalid = wc < words;
+      src.wsrc = wq + (src.wvalid ? wc : 0);
+      src.wrow_words = (size_t)words;
+    }
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
       const int row = (tid >> 4) + 8 * j;
@@ -409,7 +427,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(co
   const int st_end = (int)(((long long)(rank + 1) * KT) / S);
 
   float tot[MT][4][4];
-  mainloop<MT, kMoeExact, GROUP>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
+  mainloop<MT, kMoeExact, GROUP, RP>(src, smem_u32(smem), tid, 0, st_begin, st_end - st_begin, p.group,
                               groups, tot);
 
   float* red = reinterpret_cast<float*>(smem);
@@ -597,7 +615,7 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   return small;
 }
 
-template <int MT, int GROUP>
+template <int MT, int GROUP, bool RP>
 int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel, int nblk,
                      cudaStream_t stream) {
   constexpr int smem = Cfg<MT>::kSmemBytes;
@@ -606,9 +624,9 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
   if (!attr_done[dev]) {
-    if (cudaFuncSetAttribute(moe_gemm1_kernel<MT, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(moe_gemm1_kernel<MT, GROUP, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem) != cudaSuccess ||
-        cudaFuncSetAttribute(moe_gemm2_kernel<MT, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(moe_gemm2_kernel<MT, GROUP, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem) != cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
@@ -618,7 +636,7 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
                   act, numel, a.topk, a.H, a.I, a.group};
     const int slabs = (a.I + 127) / 128;
     const int S = pick_cluster(slabs * nblk, a.H / kBK);
-    if (int rc = launch_clustered(moe_gemm1_kernel<MT, GROUP>, p, dim3(S, slabs, nblk), S, smem, stream))
+    if (int rc = launch_clustered(moe_gemm1_kernel<MT, GROUP, RP>, p, dim3(S, slabs, nblk), S, smem, stream))
       return rc;
   }
   {
@@ -626,7 +644,7 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
                   a.num_post_pad, pair_out, numel, a.H, a.I, a.group};
     const int slabs = (a.H + kBN - 1) / kBN;
     const int S = pick_cluster(slabs * nblk, a.I / kBK);
-    if (int rc = launch_clustered(moe_gemm2_kernel<MT, GROUP>, p, dim3(S, slabs, nblk), S, smem, stream))
+    if (int rc = launch_clustered(moe_gemm2_kernel<MT, GROUP, RP>, p, dim3(S, slabs, nblk), S, smem, stream))
       return rc;
   }
   return AWQ_B200_OK;
@@ -634,6 +652,8 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
 
 int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream) {
+  // the decode-layout copy is read by the streaming kernels only (group 128, K % 128)
+  if (a.decode_layout && (a.block == 128 || a.group != 128)) return AWQ_B200_ERR_SHAPE;
   if (a.block == 128) return launch_moe_experts_tc(a, workspace, workspace_bytes, stream);
   const size_t need = moe_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
   if (workspace == nullptr || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
@@ -650,12 +670,15 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
       return AWQ_B200_ERR_LAUNCH;
   }
   int rc;
-  if (a.group == 128)
-    rc = a.block == 8 ? launch_moe_gemms<1, 128>(a, act, pair_out, numel, nblk, stream)
-                      : launch_moe_gemms<2, 128>(a, act, pair_out, numel, nblk, stream);
+  if (a.decode_layout)
+    rc = a.block == 8 ? launch_moe_gemms<1, 128, true>(a, act, pair_out, numel, nblk, stream)
+                      : launch_moe_gemms<2, 128, true>(a, act, pair_out, numel, nblk, stream);
+  else if (a.group == 128)
+    rc = a.block == 8 ? launch_moe_gemms<1, 128, false>(a, act, pair_out, numel, nblk, stream)
+                      : launch_moe_gemms<2, 128, false>(a, act, pair_out, numel, nblk, stream);
   else
-    rc = a.block == 8 ? launch_moe_gemms<1, 0>(a, act, pair_out, numel, nblk, stream)
-                      : launch_moe_gemms<2, 0>(a, act, pair_out, numel, nblk, stream);
+    rc = a.block == 8 ? launch_moe_gemms<1, 0, false>(a, act, pair_out, numel, nblk, stream)
+                      : launch_moe_gemms<2, 0, false>(a, act, pair_out, numel, nblk, stream);
   if (rc) return rc;
   {
     const long long work = (long long)a.T * (a.H / 8);

@@ -169,3 +169,30 @@ def test_fused_moe_full_size_rows_are_independent(A):
     torch.cuda.synchronize()
     assert torch.isfinite(big.float()).all()
     assert O.rel_err(big[:48].cpu().numpy(), small.float().cpu().numpy()) < 5e-3
+
+
+@pytest.mark.parametrize("t,h,i,e,k", [(1, 2048, 768, 128, 8), (16, 2048, 768, 128, 8),
+                                       (8, 256, 128, 50, 2), (40, 512, 256, 12, 2),
+                                       (256, 2048, 768, 128, 8), (300, 512, 256, 4, 2)])
+def test_experts_on_decode_layout_copies_equal_checkpoint_layout(A, t, h, i, e, k):
+    """fused_experts with the decode-layout copies of the expert weights: bit-identical to the
+    checkpoint layout where the streaming kernels run (blocks of 8 / 16 rows), and the copies
+    are simply not used where the grouped tcgen05 GEMMs run (last case)."""
+    from awq_b200 import synth
+    w1, w2 = synth.moe_layer_tensors(e, h, i, 128, seed=t + e)
+    w1 = tuple(a.cuda() for a in w1)
+    w2 = tuple(a.cuda() for a in w2)
+    x = synth.activations(t, h, seed=t).cuda()
+    logits = synth.gating_logits(t, e, seed=e).cuda()
+    w, ids, _ = A.fused_topk(x, logits, k, True)
+    d1, d2 = A.awq_repack(w1[0]), A.awq_repack(w2[0])
+    assert d1.shape == w1[0].shape and d2.shape == w2[0].shape
+    y0 = A.fused_experts(x, w1, w2, w, ids)
+    y1 = A.fused_experts(x, w1, w2, w, ids, w1_decode=d1, w2_decode=d2)
+    torch.cuda.synchronize()
+    assert torch.equal(y0, y1)
+    ref = O.fused_experts_fp32(x.cpu().numpy(), *[a.cpu().numpy() for a in w1],
+                          *[a.cpu().numpy() for a in w2], w.cpu().numpy(), ids.cpu().numpy(), 128)
+    assert O.rel_err(y1.cpu().numpy(), ref) < TOL
+    with pytest.raises(ValueError):
+        A.fused_experts(x, w1, w2, w, ids, w1_decode=d1)
