@@ -459,6 +459,9 @@ def run_moe(dev, stream):
     w1, w2 = synth.moe_layer_tensors(e, h, i, GROUP)
     w1 = tuple(a.to(dev) for a in w1)
     w2 = tuple(a.to(dev) for a in w2)
+    d1, d2 = awq_b200.awq_repack(w1[0]), awq_b200.awq_repack(w2[0])
+    from awq_b200 import _lib
+    block_of = lambda t: _lib.load().awq_b200_moe_block_size(t, k, e, h, i, GROUP)  # noqa: E731
     out = []
     for t in synth.MOE_TOKENS:
         x = synth.activations(t, h).to(dev)
@@ -468,9 +471,17 @@ def run_moe(dev, stream):
         sec = graph_time([lambda: awq_b200.fused_moe(x, w1, w2, logits, k, True)], stream,
                          reps=5 if t >= 1024 else 20)
         byts = hit * (2359296 + 73728 + 18432) + t * h * 2 * 2
-        out.append({"T": t, "experts_hit": hit, "us": round(sec * 1e6, 1),
-                    "GBps": round(byts / sec / 1e9, 1),
-                    "TFLOPs": round(t * 75497472 / sec / 1e12, 2)})
+        row = {"T": t, "experts_hit": hit, "us": round(sec * 1e6, 1),
+               "GBps": round(byts / sec / 1e9, 1),
+               "TFLOPs": round(t * 75497472 / sec / 1e12, 2)}
+        if block_of(t) in (8, 16):
+            # the same layer with the optional decode-layout copies of the expert weights
+            def layer():
+                w, ids2, _ = awq_b200.fused_topk(x, logits, k, True)
+                return awq_b200.fused_experts(x, w1, w2, w, ids2, w1_decode=d1, w2_decode=d2)
+            sd = graph_time([layer], stream, reps=20)
+            row["us_decode_layout"] = round(sd * 1e6, 1)
+        out.append(row)
     return out
 
 
