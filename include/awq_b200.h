@@ -152,7 +152,7 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * num_post_pad are the outputs of awq_b200_moe_align_block_size with block =
  * awq_b200_moe_block_size(T, topk, E, H, I, group): 8 or 16 (weight-streaming kernels; 8 while an
  * expert sees at most eight rows on average) for decode-size batches, 128 (tcgen05 grouped GEMMs)
- * once an expert sees about 32 rows or more on average.
+ * once an expert sees 36 rows or more on average.
  * Replaces fused_experts / fused_experts_impl (fused_moe/fused_moe.py:1587-1631,1664-1869)
  * and the Marlin expert path (fused_moe/experts/marlin_moe.py:225-262).
  * E is the number of stacked (local) experts.  `expert_parallel` is a set of flags: bit 0 says

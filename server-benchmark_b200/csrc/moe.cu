@@ -583,14 +583,16 @@ int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H,
   return AWQ_B200_OK;
 }
 
-// Row block of the permutation: 128 (tcgen05 grouped GEMMs) once an expert sees about 32 rows
-// or more on average and the shapes fit that kernel's tiles; 8 up to eight rows per expert on
+// Row block of the permutation: 128 (tcgen05 grouped GEMMs) once an expert sees 36 rows or more
+// on average and the shapes fit that kernel's tiles (measured at 128 experts, top-8: the grouped
+// kernels take 271 us from T = 256 to 768, the streaming kernels 169 / 215 / 254 / 336 us at
+// T = 256 / 384 / 512 / 768); 8 up to eight rows per expert on
 // average (one 8-token tile streams a third faster than two, which outweighs the experts that
 // need a second block up to there: measured crossover between T = 128 and 192 at 128 experts,
 // top-8); else 16.
 int moe_block_size(int T, int topk, int E, int H, int I, int group) {
   const long long pairs = (long long)T * topk;
-  if (pairs >= 32LL * E && moe_tc_supported(H, I, group)) return 128;
+  if (pairs >= 36LL * E && moe_tc_supported(H, I, group)) return 128;
   return pairs <= 8LL * E ? 8 : 16;
 }
 
