@@ -138,6 +138,10 @@ def awq_repack(qweight: torch.Tensor) -> torch.Tensor:
         rc = _lib.load().awq_b200_repack_qweight(qweight.data_ptr(), out.data_ptr(),
                                                  qweight.numel() // words, words * 8, _stream())
         _lib.check("awq_b200_repack_qweight", rc)
+        # Load-time operation: finish it here.  The GEMM kernels prefetch weights before they
+        # wait for the kernel ahead of them in the stream, so a copy still being written must
+        # not be handed to them.
+        torch.cuda.current_stream().synchronize()
     return out
 
 
