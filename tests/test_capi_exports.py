@@ -103,3 +103,43 @@ def test_missing_library_fails_loudly(monkeypatch, built_library):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libawq_b200.so")
     with pytest.raises(ImportError, match="no fallback"):
         _lib.load()
+
+
+def test_repack_and_block_size_host_logic(built_library):
+    """Host-side checks of the decode-layout repack and the MoE row-block choice (no GPU)."""
+    from awq_b200 import _lib
+    lib = _lib.load()
+    buf = (ctypes.c_char * 4096)()
+    p = (ctypes.addressof(buf) + 255) & ~255
+    assert lib.awq_b200_repack_qweight(None, p, 8, 8, None) == -1
+    assert lib.awq_b200_repack_qweight(p, p + 1024, 6, 8, None) == -2      # K % 4
+    assert lib.awq_b200_repack_qweight(p, p + 1024, 8, 12, None) == -2     # N % 8
+    assert lib.awq_b200_repack_qweight(p + 4, p + 1024, 8, 8, None) == -3  # alignment
+    # Qwen3-30B-A3B shapes: 8-row blocks up to eight rows per expert on average, 16-row blocks up
+    # to 36, grouped tcgen05 GEMMs (128) from there on
+    e, h, i, k = 128, 2048, 768, 8
+    assert [lib.awq_b200_moe_block_size(t, k, e, h, i, 128) for t in (1, 16, 128, 129, 512, 575, 576,
+                                                                     4096)] == \
+        [8, 8, 8, 16, 16, 16, 128, 128]
+    # shapes the grouped tcgen05 kernels do not tile stay on the streaming kernels
+    assert lib.awq_b200_moe_block_size(4096, k, e, 2048 + 128, i, 128) == 16
+
+
+def test_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: one JSON line with the keys the contract names."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference",
+                          "--steps", "1", "--warmup", "0"], capture_output=True, text=True,
+                         timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference"
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step",
+                "higher_is_better", "scaling", "vs_baseline", "dtype", "data", "config",
+                "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] in ("port", "reference")
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
