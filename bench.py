@@ -287,9 +287,11 @@ def run_cuda(args):
             if landed[j] is not None:
                 landed[j].synchronize()  # outputs of the step that last used these buffers
             with torch.cuda.stream(side[j]):
-                for layer, xp, yp in zip(layers, x_pin, y_pins[j]):
-                    xd = xp.to(dev, non_blocking=True)
-                    y = method.apply(layer, xd)
+                # inputs up, the four linears back to back (consecutive kernels of the library
+                # overlap their start-up with the end of the one before), outputs down
+                xds = [xp.to(dev, non_blocking=True) for xp in x_pin]
+                ys = [method.apply(layer, xd) for layer, xd in zip(layers, xds)]
+                for yp, y in zip(y_pins[j], ys):
                     yp.copy_(y, non_blocking=True)
                 landed[j] = torch.cuda.Event()
                 landed[j].record(side[j])
