@@ -85,6 +85,7 @@ int awq_b200_dequantize(const void* qweight, const void* scales, const void* qze
 #define AWQ_B200_KERNEL_TS_EXACT 6 /* the same with the magic-number conversion */
 #define AWQ_B200_KERNEL_WT 7       /* any M: dequantised weights registers -> TMEM (A operand), x via TMA as B */
 #define AWQ_B200_KERNEL_STREAM_RP 8 /* M <= 8 streaming kernel; `qweight` is the output of awq_b200_repack_qweight */
+#define AWQ_B200_KERNEL_Q8 9 /* M <= 32: `qweight` is the output of awq_b200_repack_kmajor; nibbles widened by tcgen05.cp, int8 MMAs */
 
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel);
 
@@ -100,6 +101,29 @@ size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel)
  */
 int awq_b200_repack_qweight(const void* qweight, void* out, int K, int N, void* stream);
 
+/*
+ * Load-time repack of qweight for AWQ_B200_KERNEL_Q8: the same nibbles, running along K instead of
+ * along N, in tiles of 256 output columns x 128 k (one quantisation group) = 16 KB, tiles ordered
+ * column slab outermost, group inside; row r of a tile is column 256 * slab + r, byte b of the row
+ * holds k = 2 b (low nibble) and 2 b + 1 of the group.  Columns past N in the last slab are zero.
+ * out: awq_b200_repack_kmajor_bytes(K, N) bytes, 32-byte aligned (0 = shape not supported).
+ * Requires K % 128 == 0, N % 8 == 0; scales and qzeros are used as they are.
+ * Counterpart in the reference stack: the load-time Marlin repack
+ * (quantization/awq_marlin.py:491-499, awq_marlin.py:90-165), whose decode kernel this replaces.
+ *
+ * With that copy, awq_b200_gemm(kernel = AWQ_B200_KERNEL_Q8) never touches a weight from a
+ * thread: TMA lays the packed nibbles into shared memory, tcgen05.cp widens them to bytes on the
+ * way into tensor memory, tcgen05.mma.kind::i8 multiplies them with the activations rewritten
+ * as 24-bit fixed point per token (three signed byte digits; a first small kernel of the call
+ * does that), and only the per-group scale / zero fold runs on the CUDA cores.  M <= 32, group 128,
+ * K <= 32768.  Its scratch (awq_b200_gemm_workspace_bytes with this kernel id) holds the digits and
+ * the partial tiles CTAs hand to each other; calls that may overlap on the GPU need separate
+ * scratch buffers.
+ */
+size_t awq_b200_repack_kmajor_bytes(int K, int N);
+
+int awq_b200_repack_kmajor(const void* qweight, void* out, int K, int N, void* stream);
+
 int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const void* qzeros,
                   const void* bias, void* out, int M, int N, int K, int group, int kernel,
                   void* workspace, size_t workspace_bytes, void* stream);
@@ -111,6 +135,21 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
  * Synchronises the device (a plain device-to-host copy).  No counterpart in the reference.
  */
 int awq_b200_device_status(int* status);
+
+/*
+ * The same, and the word is put back to 0 afterwards.  The word is sticky: it keeps the first
+ * wait that ran out (31-35: the AWQ_B200_KERNEL_Q8 kernel; 35 = a CTA waited in vain for a
+ * partial tile of another CTA) until it is cleared here, and a call during which a wait ran out
+ * still returns AWQ_B200_OK with an incomplete output.  No counterpart in the reference.
+ */
+int awq_b200_device_status_clear(int* status);
+
+/*
+ * Number of polls after which a CTA of the AWQ_B200_KERNEL_Q8 kernel stops waiting for another
+ * CTA's partial tile (0 restores the default, 2^20).  Process-wide; meant for tests that check the
+ * give-up path with a tiny limit.  No counterpart in the reference.
+ */
+void awq_b200_set_wait_limit(unsigned int polls);
 
 /*
  * Router: softmax over E experts, top-k (ties: lower expert id first), optional

@@ -120,6 +120,26 @@ def awq_gemm_fp32_torch(x, qweight, scales, qzeros, group: int = 128):
     return x.to(torch.float32) @ w
 
 
+def pack_kmajor(qweight, group: int = 128) -> np.ndarray:
+    """The K-major load-time copy of ``qweight`` that ``awq_b200_repack_kmajor`` produces, as
+    bytes: tiles of 256 output columns x one group of 128 k, column slab outermost, group inside;
+    row r of a tile is column 256 * slab + r, byte b of the row holds k = 2 b (low nibble) and
+    k = 2 b + 1 (high nibble) of the group; columns past N are zero.
+
+    The layout is this repository's own (the reference stack's counterpart is the Marlin repack,
+    awq_marlin.py:491-499, a different layout); the values it permutes are those of
+    ``unpack_awq`` (awq_triton.py:54-67), which is what pins it.
+    """
+    q = unpack_awq(qweight)
+    k, n = q.shape
+    assert group == 128 and k % 128 == 0
+    npad = -(-n // 256) * 256
+    qp = np.zeros((k, npad), dtype=np.uint8)
+    qp[:, :n] = q
+    t = qp.reshape(k // 128, 128, npad // 256, 256).transpose(2, 0, 3, 1)  # slab, group, row, k
+    return np.ascontiguousarray((t[..., 0::2] | (t[..., 1::2] << 4)).astype(np.uint8)).reshape(-1)
+
+
 def awq_linear(x, qweight, scales, qzeros, bias=None, group: int = 128) -> np.ndarray:
     """AWQLinearMethod.apply: fp16 output, optional bias added after the product.
 

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint, c_void_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 # AWQ_B200_LIBRARY points at an alternative build of the same library (kernel tuning experiments)
@@ -23,6 +23,7 @@ KERNEL_TS = 5
 KERNEL_TS_EXACT = 6
 KERNEL_WT = 7
 KERNEL_STREAM_RP = 8
+KERNEL_Q8 = 9
 
 # name -> (restype, argtypes); kept in step with include/awq_b200.h
 PROTOTYPES = {
@@ -35,6 +36,10 @@ PROTOTYPES = {
     "awq_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "awq_b200_device_status": (c_int, [POINTER(c_int)]),
+    "awq_b200_device_status_clear": (c_int, [POINTER(c_int)]),
+    "awq_b200_set_wait_limit": (None, [c_uint]),
+    "awq_b200_repack_kmajor_bytes": (c_size_t, [c_int, c_int]),
+    "awq_b200_repack_kmajor": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "awq_b200_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_void_p]),
     "awq_b200_moe_sorted_capacity": (c_int64, [c_int64, c_int, c_int]),

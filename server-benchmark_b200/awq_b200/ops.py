@@ -39,11 +39,17 @@ def _require(t: torch.Tensor, name: str, dtype, ndim: int | None = None) -> None
         raise ValueError(f"{name} must be contiguous")
 
 
-def _awq_dims(qweight, scales, qzeros):
+def _awq_dims(qweight, scales, qzeros, kmajor: bool = False):
     _require(qweight, "qweight", torch.int32, 2)
     _require(scales, "scales", torch.float16, 2)
     _require(qzeros, "qzeros", torch.int32, 2)
     k, words = qweight.shape
+    if kmajor:
+        # output of awq_repack_kmajor: [K, ceil(N / 256) * 256 / 8], the true N is that of scales
+        n = scales.shape[1]
+        if n % PACK_FACTOR or words != -(-n // 256) * 256 // PACK_FACTOR:
+            raise ValueError("qweight is not the k-major copy of a matrix with scales' width")
+        words = n // PACK_FACTOR
     n = words * PACK_FACTOR
     groups = scales.shape[0]
     if groups == 0 or k == 0 or k % groups != 0:
@@ -90,7 +96,7 @@ def awq_gemm(input: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
     ``split_k_iters`` is accepted and ignored (the split along K is chosen from the shape and
     the SM count).  ``bias`` and ``kernel`` are keyword-only extensions.
     """
-    k, n, group = _awq_dims(qweight, scales, qzeros)
+    k, n, group = _awq_dims(qweight, scales, qzeros, kmajor=kernel == _lib.KERNEL_Q8)
     _require(input, "input", torch.float16, 2)
     if input.shape[1] != k:
         raise ValueError(f"input has K={input.shape[1]}, qweight has K={k}")
@@ -142,6 +148,31 @@ def awq_repack(qweight: torch.Tensor) -> torch.Tensor:
         # wait for the kernel ahead of them in the stream, so a copy still being written must
         # not be handed to them.
         torch.cuda.current_stream().synchronize()
+    return out
+
+
+def awq_repack_kmajor(qweight: torch.Tensor) -> torch.Tensor:
+    """K-major copy of ``qweight`` for ``awq_gemm(..., kernel=KERNEL_Q8)`` (up to 32 tokens).
+
+    The same nibbles running along K, in 16 KB tiles of 256 output columns x one quantisation
+    group, column slabs outermost (include/awq_b200.h, awq_b200_repack_kmajor).  Returned as
+    int32 [K, ceil(N / 256) * 256 / 8]: the size of ``qweight`` when N is a multiple of 256.
+    K must be a multiple of 128.  Load-time counterpart of the Marlin repack in
+    vllm/model_executor/layers/quantization/awq_marlin.py:491-499.
+    """
+    _require(qweight, "qweight", torch.int32, 2)
+    k, words = qweight.shape
+    n = words * PACK_FACTOR
+    lib = _lib.load()
+    nbytes = int(lib.awq_b200_repack_kmajor_bytes(k, n))
+    if nbytes == 0:
+        raise ValueError("K must be a positive multiple of 128")
+    out = torch.empty((k, nbytes // (4 * k)), dtype=torch.int32, device=qweight.device)
+    rc = lib.awq_b200_repack_kmajor(qweight.data_ptr(), out.data_ptr(), k, n, _stream())
+    _lib.check("awq_b200_repack_kmajor", rc)
+    # load-time operation: the GEMM kernels prefetch weights before they wait for the kernel
+    # ahead of them in the stream, so the copy must be complete before it is handed to them
+    torch.cuda.current_stream().synchronize()
     return out
 
 

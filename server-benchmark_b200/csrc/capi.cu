@@ -95,8 +95,24 @@ int awq_b200_repack_qweight(const void* qweight, void* out, int K, int N, void* 
                                     static_cast<cudaStream_t>(stream));
 }
 
+size_t awq_b200_repack_kmajor_bytes(int K, int N) {
+  if (K <= 0 || N <= 0 || N % awq::kPack != 0 || K % 128 != 0) return 0;
+  return awq::repack_kmajor_bytes(K, N);
+}
+
+int awq_b200_repack_kmajor(const void* qweight, void* out, int K, int N, void* stream) {
+  if (!qweight || !out) return AWQ_B200_ERR_NULL;
+  if (K <= 0 || N <= 0 || N % awq::kPack != 0 || K % 128 != 0) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(qweight) || (reinterpret_cast<uintptr_t>(out) & 31u) != 0)
+    return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  return awq::launch_repack_kmajor(static_cast<const uint32_t*>(qweight), out, K, N,
+                                   static_cast<cudaStream_t>(stream));
+}
+
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel) {
   if (M <= 0 || check_awq_shape(N, K, group) != AWQ_B200_OK) return 0;
+  if (kernel == AWQ_B200_KERNEL_Q8) return awq::gemm_q8_workspace_bytes(M, N, K, group);
   if (kernel == AWQ_B200_KERNEL_AUTO) kernel = pick_gemm_kernel(M, N, K, group);
   if (kernel == AWQ_B200_KERNEL_TCGEN05) return awq::gemm_tc_workspace_bytes(M, N, K, group);
   return 0;
@@ -143,6 +159,15 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
     case AWQ_B200_KERNEL_WT:
       if (!awq::gemm_wt_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
       return awq::launch_gemm_wt(xh, qw, sc, qz, bh, oh, M, N, K, group, st);
+    case AWQ_B200_KERNEL_Q8: {
+      if (!awq::gemm_q8_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
+      if ((reinterpret_cast<uintptr_t>(qweight) & 31u) != 0) return AWQ_B200_ERR_ALIGN;
+      const size_t need = awq::gemm_q8_workspace_bytes(M, N, K, group);
+      if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
+      if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AWQ_B200_ERR_ALIGN;
+      return awq::launch_gemm_q8(xh, qweight, sc, qz, bh, oh, M, N, K, group, workspace,
+                                 workspace_bytes, st);
+    }
     case AWQ_B200_KERNEL_TCGEN05: {
       if (!awq::gemm_tc_supported(M, N, K, group)) return AWQ_B200_ERR_SHAPE;
       const size_t need = awq::gemm_tc_workspace_bytes(M, N, K, group);
@@ -158,16 +183,25 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
   }
 }
 
-int awq_b200_device_status(int* status) {
+static int device_status(int* status, int clear) {
   if (!status) return AWQ_B200_ERR_NULL;
   if (int rc = check_device()) return rc;
-  int a = 0, b = 0, c = 0;
-  if (int rc = awq::tc_device_status(&a)) return rc;
-  if (int rc = awq::ts_device_status(&b)) return rc;
-  if (int rc = awq::wt_device_status(&c)) return rc;
-  *status = a != 0 ? a : (b != 0 ? b : c);
+  int v[4] = {0, 0, 0, 0};
+  if (int rc = awq::tc_device_status(&v[0], clear)) return rc;
+  if (int rc = awq::ts_device_status(&v[1], clear)) return rc;
+  if (int rc = awq::wt_device_status(&v[2], clear)) return rc;
+  if (int rc = awq::q8_device_status(&v[3], clear)) return rc;
+  *status = 0;
+  for (int i = 0; i < 4; ++i)
+    if (v[i] != 0 && *status == 0) *status = v[i];
   return AWQ_B200_OK;
 }
+
+int awq_b200_device_status(int* status) { return device_status(status, 0); }
+
+int awq_b200_device_status_clear(int* status) { return device_status(status, 1); }
+
+void awq_b200_set_wait_limit(unsigned int polls) { awq::q8_set_spin_limit(polls); }
 
 int awq_b200_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                           int renormalize, float* topk_weights, int32_t* topk_ids,

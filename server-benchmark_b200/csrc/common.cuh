@@ -156,7 +156,7 @@ int launch_gemm_tc(const __half* x, const uint32_t* qweight, const __half* scale
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
-int tc_device_status(int* out);
+int tc_device_status(int* out, int clear);
 int launch_tc_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
                       const __half* scales, const uint32_t* qzeros, const float* topk_weights,
                       const int32_t* sorted_ids, const int32_t* expert_ids,
@@ -173,14 +173,26 @@ bool gemm_ts_supported(int M, int N, int K, int group);
 int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scales,
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, bool exact, cudaStream_t stream);
-int ts_device_status(int* out);
+int ts_device_status(int* out, int clear);
 
 // gemm_wt.cu: dequantised weights in tensor memory as the A operand, activations as B
 bool gemm_wt_supported(int M, int N, int K, int group);
 int launch_gemm_wt(const __half* x, const uint32_t* qweight, const __half* scales,
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, cudaStream_t stream);
-int wt_device_status(int* out);
+int wt_device_status(int* out, int clear);
+
+// gemm_q8.cu: K-major nibble copy of the weights, widened to bytes by tcgen05.cp on the way into
+// tensor memory, int8 MMAs against fixed-point activations (M <= 32)
+bool gemm_q8_supported(int M, int N, int K, int group);
+size_t repack_kmajor_bytes(int K, int N);
+int launch_repack_kmajor(const uint32_t* qweight, void* out, int K, int N, cudaStream_t stream);
+size_t gemm_q8_workspace_bytes(int M, int N, int K, int group);
+int launch_gemm_q8(const __half* x, const void* qweight_km, const __half* scales,
+                   const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
+                   int group, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+void q8_set_spin_limit(uint32_t polls);
+int q8_device_status(int* out, int clear);
 bool moe_wt_supported(int H, int I, int group);
 int launch_wt_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
                       const __half* scales, const uint32_t* qzeros, const float* topk_weights,

@@ -676,11 +676,6 @@ int launch_tc_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t*
   return launch_kernel<256, 1, 2>(map_a, map_w, p, dim3(nblk, N / 256, 1), 1, stream);
 }
 
-int tc_device_status(int* out) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
-  *out = v;
-  return AWQ_B200_OK;
-}
+int tc_device_status(int* out, int clear) { return read_tc_status(out, clear); }
 
 }  // namespace awq

@@ -638,11 +638,6 @@ int launch_gemm_ts(const __half* x, const uint32_t* qweight, const __half* scale
   return exact ? launch_ts<true>(map_w, map_x, p, stream) : launch_ts<false>(map_w, map_x, p, stream);
 }
 
-int ts_device_status(int* out) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
-  *out = v;
-  return AWQ_B200_OK;
-}
+int ts_device_status(int* out, int clear) { return read_tc_status(out, clear); }
 
 }  // namespace awq

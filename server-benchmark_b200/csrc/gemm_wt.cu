@@ -649,11 +649,6 @@ int launch_wt_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t*
   return launch_wt_kernel<128, 2>(map_w, map_x, p, dim3(1, N / kWtBN, nblk), 1, stream);
 }
 
-int wt_device_status(int* out) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
-  *out = v;
-  return AWQ_B200_OK;
-}
+int wt_device_status(int* out, int clear) { return read_tc_status(out, clear); }
 
 }  // namespace awq

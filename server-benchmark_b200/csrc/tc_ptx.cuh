@@ -12,6 +12,20 @@ namespace awq {
 // that includes this header; each file exports a reader for its own copy.
 static __device__ int g_tc_status = 0;
 
+// Host side: read this translation unit's status word; `clear` puts it back to 0 afterwards.
+// The word is sticky: it keeps the first wait that ran out until it is cleared.
+inline int read_tc_status(int* out, int clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
+  if (clear && v != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)) != cudaSuccess)
+      return AWQ_B200_ERR_LAUNCH;
+  }
+  *out = v;
+  return AWQ_B200_OK;
+}
+
 namespace tc {
 
 constexpr uint32_t kSpinLimit = 1u << 20;
