@@ -48,6 +48,7 @@ extern "C" {
 #define AWQ_B200_ERR_DEVICE (-7)    /* current device is not compute capability 10.x */
 #define AWQ_B200_ERR_DRIVER (-8)    /* a driver entry point (tensor-map encode) is unavailable */
 #define AWQ_B200_ERR_LIMIT (-9)     /* a size exceeds a fixed built-in capacity */
+#define AWQ_B200_ERR_SYMBOL (-10)   /* the built-in scratch array could not be bound on this GPU */
 
 /* Human-readable text for a return code.  Never NULL. */
 const char* awq_b200_strerror(int code);
@@ -199,7 +200,12 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * contribute zero; bit 1 says w13_q and w2_q are decode-layout copies (awq_b200_repack_qweight
  * over all E * H, respectively E * I, stacked rows), which only the weight-streaming kernels
  * read: block 8 or 16 and group 128, anything else returns AWQ_B200_ERR_SHAPE.
- * Scratch: awq_b200_moe_workspace_bytes(T, topk, E_global, H, I) bytes, 256-byte aligned.
+ * Scratch, 256-byte aligned: the activation and per-pair buffers are laid out for
+ * round_up(sorted_capacity, block) rows, so the size needed follows the sorted_capacity passed
+ * here.  awq_b200_moe_workspace_bytes(T, topk, E', H, I) bounds it when sorted_capacity is
+ * awq_b200_moe_sorted_capacity(T * topk, E', block) - with E' the expert count the permutation
+ * was built for (the global count under expert parallelism, else E).  A buffer smaller than the
+ * layout returns AWQ_B200_ERR_WORKSPACE before anything is launched.
  * Requires H % 128 == 0, I % 128 == 0, group in {32, 64, 128}.
  */
 int awq_b200_moe_block_size(int T, int topk, int E, int H, int I, int group);
@@ -222,16 +228,20 @@ int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, co
  * of its own and must not call the CUDA allocation routines from its request loop.
  *
  * The activation and per-pair buffers live in one array inside the library, in device memory,
- * awq_b200_moe_static_scratch_bytes() = 16 MiB per GPU, reserved on every GPU that loads the
- * library for as long as the process runs.  Inputs and the output are still the caller's.
+ * awq_b200_moe_static_scratch_bytes() = 16 MiB per GPU.  The CUDA runtime binds it on a GPU at
+ * the first use of the library's MoE code there (module loading is lazy) and keeps it for as long
+ * as the process runs.  Inputs and the output are still the caller's.
  * Arguments are those of awq_b200_moe_experts without workspace / workspace_bytes.
  *
- *  - A problem whose scratch need, awq_b200_moe_workspace_bytes(T, topk, E, H, I), exceeds the
- *    16 MiB is refused with AWQ_B200_ERR_LIMIT (Qwen3-30B-A3B shapes fit up to about 300
- *    tokens); use awq_b200_moe_experts with your own buffer for those.
+ *  - A problem whose scratch need exceeds the 16 MiB is refused with AWQ_B200_ERR_LIMIT before
+ *    anything is launched (Qwen3-30B-A3B shapes fit up to about 300 tokens); the need is that of
+ *    awq_b200_moe_experts and follows sorted_capacity in the same way.  Use
+ *    awq_b200_moe_experts with your own buffer for larger problems.
  *  - The call never allocates or frees device memory.  The first call on each GPU looks up the
- *    array's device address (one cudaGetSymbolAddress, cached per GPU); make that first call
- *    during start-up, before any stream capture.
+ *    array's device address (one cudaGetSymbolAddress, cached per GPU under a mutex), which is
+ *    also when the array gets bound: that first call is mandatory during start-up, while
+ *    device memory is still available and before any stream capture.  If the binding fails the
+ *    call returns AWQ_B200_ERR_SYMBOL.
  *  - All calls on one GPU share the one array and it keeps the previous call's contents.  What
  *    has to start from zero is cleared by the call itself.  Two calls that overlap on the GPU
  *    (different streams, or a graph replay racing a direct call) corrupt each other: keep calls

@@ -1,5 +1,7 @@
 // extern "C" boundary of libawq_b200.so: argument validation and kernel selection.
 // Declarations and their reference counterparts: include/awq_b200.h.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -7,10 +9,12 @@ namespace {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_device() {
+  static std::mutex mu;
   static int cc_major[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return AWQ_B200_ERR_DEVICE;
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
   if (cc_major[dev] == 0) {
     int v = 0;
     if (cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
@@ -66,6 +70,7 @@ const char* awq_b200_strerror(int code) {
     case AWQ_B200_ERR_DEVICE: return "current device is not an sm_100 GPU";
     case AWQ_B200_ERR_DRIVER: return "CUDA driver entry point unavailable";
     case AWQ_B200_ERR_LIMIT: return "size exceeds a built-in capacity";
+    case AWQ_B200_ERR_SYMBOL: return "the built-in scratch array could not be bound on this GPU";
     default: return "unknown error code";
   }
 }
@@ -249,14 +254,16 @@ size_t awq_b200_moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   return awq::moe_workspace_bytes(T, topk, E, H, I);
 }
 
-int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, const void* w13_z,
-                         const void* w2_q, const void* w2_s, const void* w2_z,
-                         const float* topk_weights, const int32_t* sorted_ids,
-                         const int32_t* expert_ids, const int32_t* num_post_pad, void* out,
-                         int T, int topk, int E, int H, int I, int group, int block,
-                         int expert_parallel, int64_t sorted_capacity, void* workspace,
-                         size_t workspace_bytes, void* stream) {
-  if (T == 0) return AWQ_B200_OK;
+// Validation shared by the two expert entry points.  Everything here is arithmetic on the
+// arguments: it runs (and refuses) before any CUDA call.  `limit` > 0: the scratch is a built-in
+// array of that size and a larger need is AWQ_B200_ERR_LIMIT; else the caller's buffer is checked.
+static int moe_validate(const void* x, const void* w13_q, const void* w13_s, const void* w13_z,
+                        const void* w2_q, const void* w2_s, const void* w2_z,
+                        const float* topk_weights, const int32_t* sorted_ids,
+                        const int32_t* expert_ids, const int32_t* num_post_pad, void* out, int T,
+                        int topk, int E, int H, int I, int group, int block, int expert_parallel,
+                        int64_t sorted_capacity, const void* workspace, size_t workspace_bytes,
+                        size_t limit, awq::MoeArgs* args) {
   if (!x || !w13_q || !w13_s || !w13_z || !w2_q || !w2_s || !w2_z || !topk_weights ||
       !sorted_ids || !expert_ids || !num_post_pad || !out)
     return AWQ_B200_ERR_NULL;
@@ -267,28 +274,51 @@ int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, co
   if ((sorted_capacity + block - 1) / block > 65535) return AWQ_B200_ERR_LIMIT;
   if (sorted_capacity < awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block))
     return AWQ_B200_ERR_WORKSPACE;
+  *args = awq::MoeArgs{static_cast<const __half*>(x),
+                       static_cast<const uint32_t*>(w13_q),
+                       static_cast<const __half*>(w13_s),
+                       static_cast<const uint32_t*>(w13_z),
+                       static_cast<const uint32_t*>(w2_q),
+                       static_cast<const __half*>(w2_s),
+                       static_cast<const uint32_t*>(w2_z),
+                       topk_weights,
+                       sorted_ids,
+                       expert_ids,
+                       num_post_pad,
+                       static_cast<__half*>(out),
+                       T, topk, E, H, I, group, block,
+                       sorted_capacity,
+                       expert_parallel & 1,
+                       (expert_parallel >> 1) & 1};
+  // the scratch need follows sorted_capacity, which the caller chose (it is at least the
+  // minimum for the stacked expert count, larger if the permutation was built for more experts)
+  const size_t need = awq::moe_layout_bytes(*args);
+  if (limit > 0) {
+    if (need > limit) return AWQ_B200_ERR_LIMIT;
+  } else {
+    if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AWQ_B200_ERR_ALIGN;
+  }
   if (!aligned16(x) || !aligned16(w13_q) || !aligned16(w13_s) || !aligned16(w13_z) ||
       !aligned16(w2_q) || !aligned16(w2_s) || !aligned16(w2_z) || !aligned16(out))
     return AWQ_B200_ERR_ALIGN;
-  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
-    return AWQ_B200_ERR_ALIGN;
+  return AWQ_B200_OK;
+}
+
+int awq_b200_moe_experts(const void* x, const void* w13_q, const void* w13_s, const void* w13_z,
+                         const void* w2_q, const void* w2_s, const void* w2_z,
+                         const float* topk_weights, const int32_t* sorted_ids,
+                         const int32_t* expert_ids, const int32_t* num_post_pad, void* out,
+                         int T, int topk, int E, int H, int I, int group, int block,
+                         int expert_parallel, int64_t sorted_capacity, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  if (T == 0) return AWQ_B200_OK;
+  awq::MoeArgs a;
+  if (int rc = moe_validate(x, w13_q, w13_s, w13_z, w2_q, w2_s, w2_z, topk_weights, sorted_ids,
+                            expert_ids, num_post_pad, out, T, topk, E, H, I, group, block,
+                            expert_parallel, sorted_capacity, workspace, workspace_bytes, 0, &a))
+    return rc;
   if (int rc = check_device()) return rc;
-  awq::MoeArgs a{static_cast<const __half*>(x),
-                 static_cast<const uint32_t*>(w13_q),
-                 static_cast<const __half*>(w13_s),
-                 static_cast<const uint32_t*>(w13_z),
-                 static_cast<const uint32_t*>(w2_q),
-                 static_cast<const __half*>(w2_s),
-                 static_cast<const uint32_t*>(w2_z),
-                 topk_weights,
-                 sorted_ids,
-                 expert_ids,
-                 num_post_pad,
-                 static_cast<__half*>(out),
-                 T, topk, E, H, I, group, block,
-                 sorted_capacity,
-                 expert_parallel & 1,
-                 (expert_parallel >> 1) & 1};
   return awq::launch_moe_experts(a, workspace, workspace_bytes,
                                  static_cast<cudaStream_t>(stream));
 }
@@ -303,39 +333,14 @@ int awq_b200_moe_experts_static(const void* x, const void* w13_q, const void* w1
                                 int H, int I, int group, int block, int expert_parallel,
                                 int64_t sorted_capacity, void* stream) {
   if (T == 0) return AWQ_B200_OK;
-  if (!x || !w13_q || !w13_s || !w13_z || !w2_q || !w2_s || !w2_z || !topk_weights ||
-      !sorted_ids || !expert_ids || !num_post_pad || !out)
-    return AWQ_B200_ERR_NULL;
-  if (T < 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0 || block <= 0) return AWQ_B200_ERR_SHAPE;
-  if (group != 128 && group != 64 && group != 32) return AWQ_B200_ERR_GROUP;
-  if (!awq::moe_supported(H, I, group, block)) return AWQ_B200_ERR_SHAPE;
-  if ((int64_t)T * topk > (1 << 24)) return AWQ_B200_ERR_LIMIT;
-  if ((sorted_capacity + block - 1) / block > 65535) return AWQ_B200_ERR_LIMIT;
-  if (sorted_capacity < awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block))
-    return AWQ_B200_ERR_WORKSPACE;
+  awq::MoeArgs a;
   // the built-in scratch has a fixed size: larger problems are refused, not truncated
-  if (awq::moe_workspace_bytes(T, topk, E, H, I) > awq::moe_static_scratch_bytes())
-    return AWQ_B200_ERR_LIMIT;
-  if (!aligned16(x) || !aligned16(w13_q) || !aligned16(w13_s) || !aligned16(w13_z) ||
-      !aligned16(w2_q) || !aligned16(w2_s) || !aligned16(w2_z) || !aligned16(out))
-    return AWQ_B200_ERR_ALIGN;
+  if (int rc = moe_validate(x, w13_q, w13_s, w13_z, w2_q, w2_s, w2_z, topk_weights, sorted_ids,
+                            expert_ids, num_post_pad, out, T, topk, E, H, I, group, block,
+                            expert_parallel, sorted_capacity, nullptr, 0,
+                            awq::moe_static_scratch_bytes(), &a))
+    return rc;
   if (int rc = check_device()) return rc;
-  awq::MoeArgs a{static_cast<const __half*>(x),
-                 static_cast<const uint32_t*>(w13_q),
-                 static_cast<const __half*>(w13_s),
-                 static_cast<const uint32_t*>(w13_z),
-                 static_cast<const uint32_t*>(w2_q),
-                 static_cast<const __half*>(w2_s),
-                 static_cast<const uint32_t*>(w2_z),
-                 topk_weights,
-                 sorted_ids,
-                 expert_ids,
-                 num_post_pad,
-                 static_cast<__half*>(out),
-                 T, topk, E, H, I, group, block,
-                 sorted_capacity,
-                 expert_parallel & 1,
-                 (expert_parallel >> 1) & 1};
   return awq::launch_moe_experts_static(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -230,6 +230,8 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I);
 int moe_block_size(int T, int topk, int E, int H, int I, int group);
 bool moe_tc_supported(int H, int I, int group);
 size_t moe_tc_workspace_bytes(int T, int topk, int E, int H, int I);
+size_t moe_tc_layout_bytes(const MoeArgs& a);
+size_t moe_layout_bytes(const MoeArgs& a);  // scratch a call with these arguments lays out
 int launch_moe_experts_tc(const MoeArgs& a, void* workspace, size_t workspace_bytes,
                           cudaStream_t stream);
 int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H,

@@ -17,6 +17,8 @@
 // memory, exactly like the dense small-M kernel.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "stream_core.cuh"
 
 namespace cg = cooperative_groups;
@@ -619,6 +621,16 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   return small;
 }
 
+// Bytes of scratch the launchers below lay out for a call: the row count comes from the caller's
+// sorted_capacity (which may exceed the minimum, e.g. a permutation built for the global expert
+// count under expert parallelism), so the size check uses exactly what the layout uses.
+size_t moe_layout_bytes(const MoeArgs& a) {
+  if (a.block == 128) return moe_tc_layout_bytes(a);
+  const int64_t rows = (a.sorted_capacity + a.block - 1) / a.block * a.block;
+  return align_up((size_t)rows * a.I * sizeof(__half), 256) +
+         align_up((size_t)a.T * a.topk * a.H * sizeof(__half), 256);
+}
+
 template <int MT, int GROUP, bool RP>
 int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel, int nblk,
                      cudaStream_t stream) {
@@ -659,7 +671,7 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
   // the decode-layout copy is read by the streaming kernels only (group 128, K % 128)
   if (a.decode_layout && (a.block == 128 || a.group != 128)) return AWQ_B200_ERR_SHAPE;
   if (a.block == 128) return launch_moe_experts_tc(a, workspace, workspace_bytes, stream);
-  const size_t need = moe_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
+  const size_t need = moe_layout_bytes(a);
   if (workspace == nullptr || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
   const int numel = a.T * a.topk;
   const int64_t rows = (a.sorted_capacity + a.block - 1) / a.block * a.block;
@@ -706,23 +718,30 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
 // cudaGetSymbolAddress (that device being current) and cached.  The lookup happens in the first
 // call on each device.
 int launch_moe_experts_static(const MoeArgs& a, cudaStream_t stream) {
-  const size_t need = moe_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
-  if (need > kMoeStaticScratchBytes) return AWQ_B200_ERR_LIMIT;
+  if (moe_layout_bytes(a) > kMoeStaticScratchBytes) return AWQ_B200_ERR_LIMIT;
+  static std::mutex mu;
   static void* scratch_addr[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
-  if (scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_moe_static_scratch) != cudaSuccess || ptr == nullptr) {
-      cudaGetLastError();
-      return AWQ_B200_ERR_LAUNCH;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (scratch_addr[dev] == nullptr) {
+      // first use of this translation unit's device globals on this GPU: with lazy module
+      // loading this is also where the 16 MiB get bound
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_moe_static_scratch) != cudaSuccess || ptr == nullptr) {
+        cudaGetLastError();
+        return AWQ_B200_ERR_SYMBOL;
+      }
+      scratch_addr[dev] = ptr;
     }
-    scratch_addr[dev] = ptr;
+    scratch = scratch_addr[dev];
   }
   // The array still holds whatever the previous call left there.  Every row the kernels read is
   // written earlier in the same call; the one region that must start at zero (per-pair outputs
   // under expert parallelism) is cleared inside launch_moe_experts.
-  return launch_moe_experts(a, scratch_addr[dev], kMoeStaticScratchBytes, stream);
+  return launch_moe_experts(a, scratch, kMoeStaticScratchBytes, stream);
 }
 
 size_t moe_static_scratch_bytes() { return kMoeStaticScratchBytes; }

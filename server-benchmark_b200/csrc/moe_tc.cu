@@ -74,10 +74,16 @@ size_t moe_tc_workspace_bytes(int T, int topk, int E, int H, int I) {
 
 int launch_moe_sum(const __half* pair_out, __half* out, int T, int topk, int H, cudaStream_t stream);
 
+size_t moe_tc_layout_bytes(const MoeArgs& a) {
+  const int64_t rows = (a.sorted_capacity + kMBM - 1) / kMBM * kMBM;
+  return align_up((size_t)rows * a.H * 2, 256) + align_up((size_t)rows * a.I * 2, 256) +
+         align_up((size_t)a.T * a.topk * a.H * 2, 256);
+}
+
 int launch_moe_experts_tc(const MoeArgs& a, void* workspace, size_t workspace_bytes,
                           cudaStream_t stream) {
   if (a.block != kMBM || !moe_tc_supported(a.H, a.I, a.group)) return AWQ_B200_ERR_SHAPE;
-  const size_t need = moe_tc_workspace_bytes(a.T, a.topk, a.E, a.H, a.I);
+  const size_t need = moe_tc_layout_bytes(a);
   if (workspace == nullptr || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
   const int numel = a.T * a.topk;
   const int64_t rows = (a.sorted_capacity + kMBM - 1) / kMBM * kMBM;

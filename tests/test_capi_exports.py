@@ -69,6 +69,37 @@ def test_host_side_validation_without_gpu(built_library):
     assert lib.awq_b200_moe_align_block_size(p, 4, 2, 8, 4, None, p, 3, p, p, None) == -5
 
 
+def test_moe_scratch_check_follows_sorted_capacity(built_library):
+    """The expert entry points lay their scratch out for round_up(sorted_capacity, block) rows.
+    Under expert parallelism the caller passes the local expert count but a permutation (and
+    sorted_capacity) built for the global one: the size check must use that capacity, and must
+    refuse before anything is launched (no GPU is needed to see the refusal)."""
+    from awq_b200 import _lib
+    lib = _lib.load()
+    buf = (ctypes.c_char * 4096)()
+    p = (ctypes.addressof(buf) + 255) & ~255
+    T, topk, e_local, e_global, H, I, block = 320, 8, 16, 128, 2048, 768, 16
+    cap = lib.awq_b200_moe_sorted_capacity(T * topk, e_global, block)
+    assert cap == T * topk + e_global * (block - 1)
+    limit = lib.awq_b200_moe_static_scratch_bytes()
+    rows = -(-cap // block) * block
+    need = -(-rows * I * 2 // 256) * 256 + -(-T * topk * H * 2 // 256) * 256
+    # the hole this closes: the layout for the local expert count's capacity fits the 16 MiB,
+    # the layout for the capacity actually passed does not
+    cap_local = lib.awq_b200_moe_sorted_capacity(T * topk, e_local, block)
+    need_local = -(-cap_local // block) * block * I * 2 + T * topk * H * 2
+    assert need_local <= limit < need
+    args = [p] * 7 + [p] * 4 + [p] + [T, topk, e_local, H, I, 128, block, 1]
+    assert lib.awq_b200_moe_experts_static(*args, cap, None) == -9
+    assert lib.awq_b200_moe_experts(*args, cap, p, limit, None) == -5
+    # a capacity far above the minimum is legal for the permutation but not for a small buffer
+    big = 4 * cap
+    assert lib.awq_b200_moe_experts_static(*args, big, None) == -9
+    assert lib.awq_b200_moe_experts(*args, big, p, need, None) == -5
+    # and the text of the new code
+    assert "scratch" in _lib.strerror(-10)
+
+
 def test_ops_reject_cpu_tensors(built_library):
     import torch
     import awq_b200

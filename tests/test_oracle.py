@@ -129,3 +129,19 @@ def test_torch_form_of_the_oracle_matches_numpy_form(golden):
         y_np = O.awq_gemm_fp32(*a, g)
         y_t = O.awq_gemm_fp32_torch(*[torch.from_numpy(v) for v in a], g).numpy()
         assert np.allclose(y_np, y_t, rtol=1e-5, atol=1e-5)
+
+
+def test_pack_kmajor_layout():
+    """The K-major repack permutes the unpacked nibbles: tile (slab, group) = 256 rows of 64 bytes,
+    row r = column 256 * slab + r, nibble j of the row = k 128 * group + j; columns past N zero."""
+    rng = np.random.default_rng(5)
+    k, n = 256, 264                     # two groups, one full slab and 8 columns of a second
+    q = rng.integers(0, 16, size=(k, n), dtype=np.int64)
+    packed = O.pack_awq(q)
+    km = O.pack_kmajor(packed).reshape(2, 2, 256, 64)        # slab, group, row, byte
+    for slab, g, r, b in [(0, 0, 0, 0), (0, 1, 255, 63), (1, 0, 7, 10), (1, 1, 3, 31)]:
+        col = 256 * slab + r
+        lo, hi = q[128 * g + 2 * b, col], q[128 * g + 2 * b + 1, col]
+        assert km[slab, g, r, b] == (lo | (hi << 4))
+    assert not km[1, :, 8:, :].any()    # padding columns
+    assert km.size == 2 * 2 * 256 * 64
