@@ -10,8 +10,7 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint, c_void_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# AWQ_B200_LIBRARY points at an alternative build of the same library (kernel tuning experiments)
-LIB_PATH = os.environ.get("AWQ_B200_LIBRARY") or os.path.join(_HERE, "libawq_b200.so")
+LIB_PATH = os.path.join(_HERE, "libawq_b200.so")
 
 OK = 0
 KERNEL_AUTO = 0

@@ -1,6 +1,8 @@
 // Shared device/host helpers for the AWQ W4A16 kernels (sm_100a only).
 #pragma once
 
+#include <atomic>
+
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>

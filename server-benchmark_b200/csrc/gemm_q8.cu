@@ -719,7 +719,7 @@ int launch_q8(const __half* x, const void* qweight_km, const __half* scales, con
               const __half* bias, __half* out, int M, int N, int K, void* workspace,
               size_t workspace_bytes, cudaStream_t stream) {
   using Cfg = Q8Cfg<MT>;
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;

@@ -27,18 +27,12 @@ struct StreamParams {
   int M, N, K, group;
 };
 
-#ifndef AWQ_STREAM_BLOCKS_MT1
-#define AWQ_STREAM_BLOCKS_MT1 5
-#endif
-#ifndef AWQ_STREAM_MIN_STAGES
-#define AWQ_STREAM_MIN_STAGES 6
-#endif
-#ifndef AWQ_STREAM_MAX_CLUSTER
-#define AWQ_STREAM_MAX_CLUSTER 8
-#endif
+constexpr int kBlocksMT1 = 5;    // resident CTAs per SM the 8-token kernel is sized for
+constexpr int kMinStages = 6;    // stages a warp group must have for a K split to pay
+constexpr int kMaxCluster = 8;   // portable cluster size
 constexpr int kPdlMinStages = 12;
 constexpr int min_blocks(int MT, int WG) {
-  return WG == 1 ? (MT == 1 ? AWQ_STREAM_BLOCKS_MT1 : (MT == 2 ? 4 : 2)) : (MT == 1 && WG <= 3 ? 2 : 1);
+  return WG == 1 ? (MT == 1 ? kBlocksMT1 : (MT == 2 ? 4 : 2)) : (MT == 1 && WG <= 3 ? 2 : 1);
 }
 
 template <int MT, bool EXACT, int GROUP, int WG, bool RP>
@@ -137,7 +131,7 @@ gemm_stream_kernel(const StreamParams p) {
 template <int MT, bool EXACT, int GROUP, int WG, bool RP = false>
 int launch_variant(const StreamParams& p, int S, cudaStream_t stream) {
   constexpr int smem = Cfg<MT>::kSmemBytes * WG;
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;
@@ -146,7 +140,7 @@ int launch_variant(const StreamParams& p, int S, cudaStream_t stream) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
-    if (AWQ_STREAM_MAX_CLUSTER > 8 &&
+    if (kMaxCluster > 8 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
             cudaSuccess)
       return AWQ_B200_ERR_LAUNCH;
@@ -182,16 +176,16 @@ template <int MT, bool EXACT, int GROUP, bool RP = false>
 int launch_split(const StreamParams& p, cudaStream_t stream) {
   const int slabs = (p.N + kBN - 1) / kBN;
   const int KT = p.K / kBK;
-  const int want = (MT == 1 ? AWQ_STREAM_BLOCKS_MT1 : 4) * sm_count();  // warp groups in flight
+  const int want = (MT == 1 ? kBlocksMT1 : 4) * sm_count();  // warp groups in flight
   int S = want / slabs;
-  S = S < 1 ? 1 : (S > AWQ_STREAM_MAX_CLUSTER ? AWQ_STREAM_MAX_CLUSTER : S);
+  S = S < 1 ? 1 : (S > kMaxCluster ? kMaxCluster : S);
   while (S > 1 && KT / S < 3) --S;
   // more warp groups per CTA when the cluster limit (8) leaves SMs under-filled
   int wg = 1;
   if (MT == 1) {
     wg = want / (slabs * S);
     wg = wg < 1 ? 1 : (wg > 3 ? 3 : wg);
-    while (wg > 1 && KT / (S * wg) < AWQ_STREAM_MIN_STAGES) --wg;
+    while (wg > 1 && KT / (S * wg) < kMinStages) --wg;
   }
   if (wg == 3) return launch_variant<MT, EXACT, GROUP, 3, RP>(p, S, stream);
   if (wg == 2) return launch_variant<MT, EXACT, GROUP, 2, RP>(p, S, stream);
@@ -215,7 +209,7 @@ int launch_by_m(const StreamParams& p, cudaStream_t stream) {
 }  // namespace
 
 int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];  // zero-initialised
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
   if (cached[dev] == 0) {
@@ -224,7 +218,7 @@ int sm_count() {
       v = 148;
     cached[dev] = v;
   }
-  return cached[dev];
+  return cached[dev].load();
 }
 
 bool gemm_stream_supported(int M, int N, int K, int group) {

@@ -529,29 +529,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
 // ---- host side -------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
 // fp16 activations [rows, cols], box [64 k x 128 rows], 128-byte swizzle
 int make_a_map(CUtensorMap* m, const __half* base, int64_t rows, int cols) {
-  EncodeTiledFn enc = encode_fn();
+  EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return AWQ_B200_ERR_DRIVER;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
@@ -566,7 +546,7 @@ int make_a_map(CUtensorMap* m, const __half* base, int64_t rows, int cols) {
 
 // packed weights [rows, words] (experts stacked along the rows), box [16 words x 64 rows]
 int make_w_map(CUtensorMap* m, const uint32_t* base, int64_t rows, int words) {
-  EncodeTiledFn enc = encode_fn();
+  EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return AWQ_B200_ERR_DRIVER;
   const cuuint64_t dims[2] = {(cuuint64_t)words, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)words * 4};
@@ -583,7 +563,7 @@ template <int BN, int MT, int MODE>
 int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const TcParams& p, dim3 grid,
                   int Z, cudaStream_t stream) {
   using C = TcCfg<BN, MT>;
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;

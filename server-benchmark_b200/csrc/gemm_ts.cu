@@ -572,7 +572,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 template <bool EXACT>
 int launch_ts(const CUtensorMap& map_w, const CUtensorMap& map_x, const TsParams& p,
               cudaStream_t stream) {
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;

@@ -547,7 +547,7 @@ template <int NT, int MODE>
 int launch_wt_kernel(const CUtensorMap& map_w, const CUtensorMap& map_x, const WtParams& p, dim3 grid,
                      int S, cudaStream_t stream) {
   using C = WtCfg<NT>;
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;

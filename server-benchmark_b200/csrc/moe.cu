@@ -635,7 +635,7 @@ template <int MT, int GROUP, bool RP>
 int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel, int nblk,
                      cudaStream_t stream) {
   constexpr int smem = Cfg<MT>::kSmemBytes;
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return AWQ_B200_ERR_DEVICE;

@@ -56,13 +56,7 @@ constexpr int kGroupThreads = 128;  // one warp group
 template <int MT>
 struct Cfg {
   // MT = 2 trades the third stage for a fourth resident CTA per SM (more warps to hide latency)
-#ifndef AWQ_STREAM_STAGES_MT1
-#define AWQ_STREAM_STAGES_MT1 2
-#endif
-#ifndef AWQ_STREAM_STAGES_MT2
-#define AWQ_STREAM_STAGES_MT2 2
-#endif
-  static constexpr int kStages = MT == 2 ? AWQ_STREAM_STAGES_MT2 : (MT == 1 ? AWQ_STREAM_STAGES_MT1 : 3);
+  static constexpr int kStages = MT <= 2 ? 2 : 3;
   static constexpr int kStageBytes = kWStageBytes + MT * 8 * kXPitch * 2;
   static constexpr int kPipeBytes = kStages * kStageBytes;
   static constexpr int kRedBytes = MT * 8 * kRedPitch * 4;

@@ -157,17 +157,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against
 // libcuda); nullptr when the driver does not provide it.
 inline EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // initialised once, thread-safely (function-local static)
+  static const EncodeTiledFn fn = [] {
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
             cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
+      return reinterpret_cast<EncodeTiledFn>(sym);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
   return fn;
 }
 

@@ -113,7 +113,7 @@ def _moe_case(e, h, i, t, k, seed):
 @pytest.mark.parametrize("e,h,i,t,k", [
     (4, 256, 128, 5, 2), (8, 512, 256, 1, 2), (16, 2048, 768, 16, 8), (128, 2048, 768, 1, 8),
     (128, 2048, 768, 40, 8), (8, 256, 128, 300, 2), (8, 512, 256, 777, 2),
-    (128, 2048, 768, 1024, 8),
+    (128, 2048, 768, 128, 8), (128, 2048, 768, 1024, 8), (128, 2048, 768, 4096, 8),
     # 8-row blocks with experts that need several blocks, and 16-row blocks
     (16, 512, 256, 60, 2), (128, 2048, 768, 200, 8), (8, 256, 128, 50, 2),
 ])

@@ -50,7 +50,7 @@ SHAPES = [
     (16, 256, 256),     # two stages
     (16, 1024, 512),    # ring wraps, two slabs
     (1, 512, 256), (3, 384, 32), (9, 640, 288),   # ragged M, N edge inside a slab
-    (16, 8192, 1024), (4, 3712, 8192), (16, 2048, 1536),
+    (16, 8192, 8192), (4, 3712, 8192), (16, 2048, 1536),
 ]
 
 
