@@ -11,12 +11,22 @@ distributions of the benchmark configuration (nibbles uniform 0..15, scales unif
 [0.002, 0.02], activations N(0,1)).
 
 metric  awq_w4a16_gemm_hbm_TBps = int4 weight bytes streamed per second, whole job.
-value   device-resident: the step is captured once in a CUDA graph and replayed; timed with
-        CUDA events on the launching stream between barriers, max over ranks.
-e2e     the same step through the layer API (AWQLinearMethod.apply) with the activations in
-        pinned host memory: host->device copy, four kernels, device->host copy of the outputs,
-        every step; weights stay resident in HBM as they do while serving.  Four steps are in
-        flight on four streams (copies of one step overlap kernels of another).
+value   device-resident: the step (AWQLinearMethod.apply of the four layers) is captured once in
+        a CUDA graph and replayed; exactly --steps replays are timed with CUDA events on the
+        launching stream between barriers, max over ranks.  The measurement is repeated until
+        it has covered about 0.6 s, so that the nvidia-smi sampler (50 ms period) sees the
+        clocks under load many times; the median repeat is reported, min and max beside it.
+e2e     the same step through the layer API with the activations in pinned host memory:
+        host->device copies, the kernels, device->host copies of the four outputs, every step;
+        weights stay resident in HBM as they do while serving.  Each in-flight step (copies
+        included) is one CUDA graph on its own stream; four are in flight, and the figure for
+        one step at a time (what a single decoding sequence sees) is reported beside it.
+layers  the layers are loaded with AWQConfig(decode_kmajor=True): gate_up keeps a K-major copy
+        of its weights and runs the kernel that widens nibbles with tcgen05.cp (2 launches:
+        activation digits + GEMM); qkv, o_proj and down run the registers->TMEM kernel.
+bars    every row of the shape sweep and of the MoE table also times the installed vLLM's own
+        kernels on the same GPU with the same protocol (awq_b200/vllm_ref.py): awq_gemm,
+        awq_dequantize + matmul, awq_marlin_repack + marlin_gemm, fused_marlin_moe.
 N > 1   replicas (the TP=1 scaling mode of the harness): every rank runs the same step on its
         own GPU, value is the sum; reported as weak scaling.  The tensor-parallel variant
         (column/row shards + NCCL all-reduce of the row-parallel outputs) is timed as well and
@@ -48,7 +58,9 @@ FALLBACK_HBM_GBS = 6650.0
 # launch's algorithmic bytes, from an ncu capture of a smaller case (K = 8192, N = 29568: 130.2 MB
 # of traffic for 126.6 MB); the traffic of the full-size launches is scaled by their bytes
 NCU_TRAFFIC_RATIO = 1.028
-E2E_DEPTH = 4  # steps in flight in the end-to-end leg (2: 0.255, 3: 0.206, 4: 0.201, 6: 0.198 ms per step)
+E2E_DEPTH = 4          # steps in flight in the end-to-end leg
+TIMED_SECONDS = 0.6    # what the repeated device-resident measurement covers at least
+ROTATE_BYTES = 400_000_000  # weight sets rotated per shape: at least this much and at least two
 
 
 def shapes():
@@ -148,9 +160,20 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 
 
+def cpu_model() -> str:
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.lower().startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except Exception:
+        pass
+    return "unknown"
+
+
 def cpu_reference_sample(reps: int):
     """Times the fp32 dequantise-then-matmul of the o_proj shape (K = N = 8192, M = 16) on the
-    host.  Returns (seconds per call (best), cores, description)."""
+    host, and the matmul alone on the already dequantised matrix.  Returns a dict with the best
+    and the mean of `reps` calls (after one warm-up) for both."""
     import torch
     from awq_b200 import synth
     from oracle import awq_oracle as O
@@ -166,28 +189,44 @@ def cpu_reference_sample(reps: int):
         t = time.perf_counter()
         O.awq_gemm_fp32_torch(x, qw, s, qz, GROUP)
         times.append(time.perf_counter() - t)
-    return min(times), sum(times) / len(times), cores, \
-        f"o_proj K=8192 N=8192 M={M_TOKENS} group 128, torch fp32 dequantise+matmul, {reps} calls"
+    w = torch.from_numpy(O.dequantize_fp32(qw.numpy(), s.numpy(), qz.numpy(), GROUP))
+    xf = x.float()
+    xf @ w
+    mm = []
+    for _ in range(max(reps, 3)):
+        t = time.perf_counter()
+        xf @ w
+        mm.append(time.perf_counter() - t)
+    return {"best": min(times), "mean": sum(times) / len(times), "cores": cores,
+            "matmul_only_best": min(mm), "cpu_model": cpu_model(),
+            "sample": f"o_proj K=8192 N=8192 M={M_TOKENS} group 128, torch fp32 "
+                      f"dequantise+matmul on {cores} threads, best and mean of {reps} calls "
+                      "after one warm-up"}
+
+
+def cpu_baseline_block(c):
+    wbytes = 8192 * 8192 // 2
+    return {"value": wbytes / c["best"] / 1e12, "unit": UNIT, "cores": c["cores"], "kind": "port",
+            "sample": c["sample"], "value_mean": wbytes / c["mean"] / 1e12,
+            "ms_best": c["best"] * 1e3, "ms_mean": c["mean"] * 1e3,
+            "matmul_only_ms_best": c["matmul_only_best"] * 1e3, "cpu_model": c["cpu_model"]}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    reps = max(1, min(args.steps, 20))
-    for _ in range(min(args.warmup, 2)):
-        pass
-    best, mean, cores, sample = cpu_reference_sample(reps)
-    wbytes = 8192 * 8192 // 2
-    val = wbytes / mean / 1e12
+    reps = max(3, min(args.steps, 20))
+    c = cpu_reference_sample(reps)
+    block = cpu_baseline_block(c)
+    val = block["value"]
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": reps, "warmup": 1, "ms_per_step": mean * 1e3, "higher_is_better": True,
+        "steps": reps, "warmup": 1, "ms_per_step": c["best"] * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "awq_w4a16_linear_M16_qwen2.5-72b_layer (sampled: o_proj shape)",
                    "group_size": GROUP, "tokens": M_TOKENS},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": sample},
+        "cpu_baseline": block,
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -216,11 +255,11 @@ def run_cuda(args):
     if rank != 0:
         awq_build.build()
     import awq_b200
-    from awq_b200 import synth, tp
+    from awq_b200 import synth, _lib
 
     dev = torch.device("cuda", local)
     m = M_TOKENS
-    method = awq_b200.AWQLinearMethod(awq_b200.AWQConfig(group_size=GROUP))
+    method = awq_b200.AWQLinearMethod(awq_b200.AWQConfig(group_size=GROUP, decode_kmajor=True))
     layers, xs = [], []
     for i, (name, (k, n)) in enumerate(shapes()):
         layer = awq_b200.AWQLinear()
@@ -234,16 +273,23 @@ def run_cuda(args):
         xs.append(synth.activations(m, k, seed=i))
     x_dev = [x.to(dev) for x in xs]
     x_pin = [x.pin_memory() for x in xs]
-    y_pin = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _, (k, n) in shapes()]
+    kernels = ["gemm_q8_kernel (+ q8_prep_kernel)" if getattr(l, "qweight_kmajor", None) is not None
+               else "gemm_ts_kernel" for l in layers]
+    launches_per_step = sum(2 if "q8" in kname else 1 for kname in kernels)
 
     def step_device():
-        for layer, x in zip(layers, x_dev):
-            awq_b200.awq_gemm(x, layer.qweight, layer.scales, layer.qzeros, 8)
+        return [method.apply(layer, x) for layer, x in zip(layers, x_dev)]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def device_status():
+        import ctypes
+        v = ctypes.c_int(-1)
+        _lib.load().awq_b200_device_status_clear(ctypes.byref(v))
+        return v.value
 
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
@@ -252,74 +298,116 @@ def run_cuda(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             step_device()
-        for _ in range(max(args.warmup, 3)):
+        warm = max(args.warmup, 3)
+        w0 = torch.cuda.Event(enable_timing=True)
+        w1 = torch.cuda.Event(enable_timing=True)
+        w0.record(stream)
+        for _ in range(warm):
             graph.replay()
+        w1.record(stream)
         barrier()
+        est = max(w0.elapsed_time(w1) * 1e-3 / warm, 1e-6)     # seconds per step, for sizing
+        repeats = int(min(200, max(5, -(-TIMED_SECONDS // (est * args.steps)))))
+        if world > 1:
+            t = torch.tensor([repeats], device=dev, dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            repeats = int(t[0])
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
             time.sleep(0.12)
-        e0 = torch.cuda.Event(enable_timing=True)
-        e1 = torch.cuda.Event(enable_timing=True)
         barrier()
         t_wall0 = time.time()
-        e0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record(stream)
-        barrier()
+        rep_ms = []
+        for _ in range(repeats):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record(stream)
+            for _ in range(args.steps):          # exactly --steps steps between the events
+                graph.replay()
+            e1.record(stream)
+            barrier()
+            rep_ms.append(e0.elapsed_time(e1))
         t_wall1 = time.time()
-        ms = e0.elapsed_time(e1)
+        if world > 1:                              # every repeat: max over ranks
+            t = torch.tensor(rep_ms, device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            rep_ms = t.tolist()
+        rep_sorted = sorted(rep_ms)
+        ms = rep_sorted[len(rep_sorted) // 2]
+        status_after_timed = device_status()
 
         # ---- e2e through the layer API with host buffers ----
-        # E2E_DEPTH steps are in flight, each on its own stream with its own pinned result
-        # buffers (a serving loop with that many requests in flight): the copies of one step
-        # overlap the kernels of another.  Every step still copies its inputs from pinned host
-        # memory and its four outputs back, and the host waits for a step's outputs before
-        # the buffers are used again.
-        side = [torch.cuda.Stream(device=dev) for _ in range(E2E_DEPTH)]
-        y_pins = [y_pin] + [[torch.empty_like(y).pin_memory() for y in y_pin]
-                            for _ in range(E2E_DEPTH - 1)]
-        landed = [None] * E2E_DEPTH
+        # One CUDA graph per in-flight step, on its own stream with its own pinned buffers:
+        # the four host->device copies, the four layers back to back, the four device->host
+        # copies.  The host waits for a slot's outputs before it launches the slot again.
+        def make_slot():
+            st = torch.cuda.Stream(device=dev)
+            xd = [torch.empty_like(x, device=dev) for x in xs]
+            yp = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _, (k, n) in shapes()]
 
-        def step_e2e(i):
-            j = i % E2E_DEPTH
-            if landed[j] is not None:
-                landed[j].synchronize()  # outputs of the step that last used these buffers
-            with torch.cuda.stream(side[j]):
-                # inputs up, the four linears back to back (consecutive kernels of the library
-                # overlap their start-up with the end of the one before), outputs down
-                xds = [xp.to(dev, non_blocking=True) for xp in x_pin]
-                ys = [method.apply(layer, xd) for layer, xd in zip(layers, xds)]
-                for yp, y in zip(y_pins[j], ys):
-                    yp.copy_(y, non_blocking=True)
-                landed[j] = torch.cuda.Event()
-                landed[j].record(side[j])
+            def body():
+                for d, h in zip(xd, x_pin):
+                    d.copy_(h, non_blocking=True)
+                ys = [method.apply(layer, d) for layer, d in zip(layers, xd)]
+                for h, y in zip(yp, ys):
+                    h.copy_(y, non_blocking=True)
 
-        def drain():
-            for j in range(E2E_DEPTH):
-                if landed[j] is not None:
-                    landed[j].synchronize()
-                stream.wait_stream(side[j])
+            with torch.cuda.stream(st):
+                body()
+                st.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    body()
+            return {"stream": st, "graph": g, "y": yp, "done": None}
 
-        e2e_steps = max(1, min(args.steps, 300))
-        for i in range(3 * E2E_DEPTH):
-            step_e2e(i)
-        drain()
-        barrier()
-        f0 = torch.cuda.Event(enable_timing=True)
-        f1 = torch.cuda.Event(enable_timing=True)
-        f0.record(stream)
-        for j in range(E2E_DEPTH):
-            side[j].wait_stream(stream)
-        for i in range(e2e_steps):
-            step_e2e(i)
-        drain()
-        f1.record(stream)
-        barrier()
-        ms_e2e = f0.elapsed_time(f1)
+        def run_e2e(depth, steps):
+            slots = [make_slot() for _ in range(depth)]
+
+            def launch(i):
+                sl = slots[i % depth]
+                if sl["done"] is not None:
+                    sl["done"].synchronize()      # the host has the outputs of the slot's last step
+                with torch.cuda.stream(sl["stream"]):
+                    sl["graph"].replay()
+                    sl["done"] = torch.cuda.Event()
+                    sl["done"].record(sl["stream"])
+
+            def drain():
+                for sl in slots:
+                    if sl["done"] is not None:
+                        sl["done"].synchronize()
+                    stream.wait_stream(sl["stream"])
+
+            for i in range(3 * depth):
+                launch(i)
+            drain()
+            barrier()
+            f0 = torch.cuda.Event(enable_timing=True)
+            f1 = torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for sl in slots:
+                sl["stream"].wait_stream(stream)
+            for i in range(steps):
+                launch(i)
+            drain()
+            f1.record(stream)
+            barrier()
+            out = f0.elapsed_time(f1)
+            ref = [y.clone() for y in slots[0]["y"]]
+            del slots
+            return out, ref
+
+        e2e_steps = max(20, min(args.steps * repeats, 2000))
+        ms_e2e, y_host = run_e2e(E2E_DEPTH, e2e_steps)
+        ms_e2e_serial, _ = run_e2e(1, max(20, e2e_steps // 4))
         if rank == 0:
             sampler.stop()
+        # the outputs that came back to the host are the ones the device-resident step produces
+        y_dev = step_device()
+        torch.cuda.synchronize()
+        e2e_matches = all(torch.equal(a, b.cpu()) for a, b in zip(y_host, y_dev))
 
         # ---- benchmark configurations 2 and 3 (1 GPU only): shape sweep and MoE layer ----
         sweep = moe = None
@@ -334,51 +422,56 @@ def run_cuda(args):
             tp_result = run_tp(args, world, rank, dev, stream, barrier)
 
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_e2e, ms_e2e_serial], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
+        ms_e2e, ms_e2e_serial = float(t[0]), float(t[1])
 
     if rank == 0:
         wbytes = weight_bytes_per_step()
         sec = ms * 1e-3 / args.steps
         value = world * wbytes / sec / 1e12
         sec_e2e = ms_e2e * 1e-3 / e2e_steps
+        sec_e2e_serial = ms_e2e_serial * 1e-3 / max(20, e2e_steps // 4)
         peak, peak_kind = measured_peak()
         achieved = wbytes / sec / 1e9  # GB/s of int4 weight bytes, one GPU
         achieved_all = all_bytes_per_step(m) / sec / 1e9
-        launches_per_step = len(layers)
-        cpu_best, cpu_mean, cores, sample = (None, None, None, None)
-        cpu = None
-        if world == 1:
-            cpu_best, cpu_mean, cores, sample = cpu_reference_sample(3)
-            cpu = {"value": (8192 * 8192 // 2) / cpu_best / 1e12, "unit": UNIT, "cores": cores,
-                   "kind": "port", "sample": sample}
+        cpu = cpu_baseline_block(cpu_reference_sample(3)) if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "repeats": repeats,
+            "ms_per_step_min": rep_sorted[0] / args.steps, "ms_per_step_max": rep_sorted[-1] / args.steps,
             "config": {"workload": "awq_w4a16_linear_M16_qwen2.5-72b_layer (qkv,o_proj,gate_up,down)",
                        "group_size": GROUP, "tokens": m, "parallelism": f"replicas x{world}",
-                       "l2": "inputs larger than L2 (438.8 MB of weights per step)"},
+                       "l2": "inputs larger than L2 (438.8 MB of weights per step)",
+                       "load_time_copies": "gate_up: K-major copy (AWQConfig(decode_kmajor=True))"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         "kernel": "gemm_ts_kernel (4 launches per step: qkv, o_proj, gate_up, "
-                                   "down); achieved = weight bytes of the step / step time",
+                         "kernel": "one step = " + ", ".join(
+                             f"{name}: {kn}" for (name, _), kn in zip(shapes(), kernels)) +
+                                   "; achieved = int4 weight bytes of the step / step time",
                          "achieved_all_bytes": achieved_all,
-                         "traffic": NCU_TRAFFIC_RATIO * all_bytes_per_step(m) / launches_per_step},
+                         "traffic": NCU_TRAFFIC_RATIO * all_bytes_per_step(m),
+                         "traffic_basis": "per step (sum of the step's launches); achieved is per "
+                                          "step as well"},
             "cpu_baseline": cpu,
             "e2e": {"value": world * wbytes / sec_e2e / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": sum(m * k * 2 for _, (k, n) in shapes()),
                     "d2h_bytes_per_step": sum(m * n * 2 for _, (k, n) in shapes()),
-                    "steps": e2e_steps, "ms_per_step": sec_e2e * 1e3, "steps_in_flight": E2E_DEPTH},
+                    "steps": e2e_steps, "ms_per_step": sec_e2e * 1e3, "steps_in_flight": E2E_DEPTH,
+                    "one_step_at_a_time_ms": sec_e2e_serial * 1e3,
+                    "one_step_at_a_time_value": world * wbytes / sec_e2e_serial / 1e12,
+                    "outputs_equal_device_resident": bool(e2e_matches)},
             "gpu_launches": launches_per_step * args.steps,
+            "device_status": status_after_timed,
             "clocks": sampler.summary(t_wall0, t_wall1),
         }
         if tp_result is not None:
             line["tp"] = tp_result
         if sweep is not None:
             tpeak = measured_tensor_peak()
-            big = max((r for r in sweep if r["M"] >= 1024), key=lambda r: r["TFLOPs"])
+            big = max((r for r in sweep if r.get("M", 0) >= 1024), key=lambda r: r["TFLOPs"])
             line["roofline_tensor"] = {"bound": "tensor", "achieved": big["TFLOPs"],
                                        "peak": tpeak[0], "unit": "TFLOP/s",
                                        "frac": big["TFLOPs"] / tpeak[0], "peak_kind": f"of {tpeak[1]}",
@@ -416,25 +509,40 @@ def graph_time(fns, stream, reps=3):
     return e0.elapsed_time(e1) * 1e-3 / (reps * len(fns))
 
 
+def _vllm_ref():
+    """awq_b200.vllm_ref if the installed vLLM's compiled ops load, else None."""
+    try:
+        from awq_b200 import vllm_ref
+        return vllm_ref if vllm_ref.available() else None
+    except Exception:
+        return None
+
+
 def run_sweep(dev, stream):
     """Benchmark configuration 2: the four 72B layer shapes x M in {1 .. 4096}, 1 GPU.  Weights are
-    rotated over enough copies that every launch reads more than the L2 holds."""
+    rotated over at least two copies and at least ROTATE_BYTES (more than three times the L2),
+    so every launch streams from HBM.  Every row also times vLLM's kernels for the same work
+    with the same protocol."""
     import torch
     import awq_b200
     from awq_b200 import synth
+    V = _vllm_ref()
     out = []
     for name, (k, n) in shapes():
         wbytes = k * n // 2
-        copies = max(1, -(-200_000_000 // wbytes))
+        copies = max(2, -(-ROTATE_BYTES // wbytes))
         base = [a.to(dev) for a in synth.awq_linear_tensors(k, n, GROUP, seed=1)]
         sets = [base] + [[a.clone() for a in base] for _ in range(copies - 1)]
         decode = [awq_b200.awq_repack(q[0]) for q in sets]
+        kmajor = [awq_b200.awq_repack_kmajor(q[0]) for q in sets]
+        marlin = [V.marlin_prepare(*q) for q in sets] if V is not None else None
         for m in synth.SWEEP_M:
             x = synth.activations(m, k).to(dev)
+            reps = 3 if m >= 1024 else 10
             fns = [(lambda q=q: awq_b200.awq_gemm(x, q[0], q[1], q[2], 8)) for q in sets]
-            t = graph_time(fns, stream, reps=3 if m >= 1024 else 10)
-            row = {"shape": name, "K": k, "N": n, "M": m, "us": round(t * 1e6, 2),
-                   "weight_GBps": round(wbytes / t / 1e9, 1),
+            t = graph_time(fns, stream, reps=reps)
+            row = {"shape": name, "K": k, "N": n, "M": m, "weight_sets": copies,
+                   "us": round(t * 1e6, 2), "weight_GBps": round(wbytes / t / 1e9, 1),
                    "TFLOPs": round(2.0 * m * k * n / t / 1e12, 2)}
             if m <= 8:
                 # the same layer with the optional decode-layout copy of qweight (made once, at
@@ -445,44 +553,102 @@ def run_sweep(dev, stream):
                 tr = graph_time(fns, stream, reps=10)
                 row["us_decode_layout"] = round(tr * 1e6, 2)
                 row["weight_GBps_decode_layout"] = round(wbytes / tr / 1e9, 1)
+            if m <= 16:
+                # ... and with the K-major copy (AWQConfig(decode_kmajor=True)): nibbles widened
+                # by tcgen05.cp, int8 MMAs
+                fns = [(lambda q=q, r=r: awq_b200.awq_gemm(x, r, q[1], q[2], 8,
+                                                          kernel=awq_b200.KERNEL_Q8))
+                       for q, r in zip(sets, kmajor)]
+                tq = graph_time(fns, stream, reps=10)
+                row["us_kmajor"] = round(tq * 1e6, 2)
+                row["weight_GBps_kmajor"] = round(wbytes / tq / 1e9, 1)
+            best = min(v for kk, v in row.items() if kk.startswith("us"))
+            if V is None:
+                row["vllm"] = "compiled ops of the installed vLLM did not load"
+            else:
+                try:
+                    if m < 256:   # the route AWQLinearMethod.apply takes below 256 tokens
+                        tv = graph_time([(lambda q=q: V.awq_gemm(x, q[0], q[1], q[2]))
+                                         for q in sets], stream, reps=max(2, reps // 2))
+                        row["vllm_awq_us"] = round(tv * 1e6, 2)
+                    else:         # ... and from 256 tokens on: dequantize + matmul
+                        tv = graph_time([(lambda q=q: V.awq_dequant_matmul(x, q[0], q[1], q[2]))
+                                         for q in sets], stream, reps=2)
+                        row["vllm_dequant_matmul_us"] = round(tv * 1e6, 2)
+                    tm = graph_time([(lambda mq=mq: V.marlin_gemm(x, mq)) for mq in marlin],
+                                    stream, reps=max(2, reps // 2))
+                    row["vllm_marlin_us"] = round(tm * 1e6, 2)
+                    row["speedup_vs_vllm_marlin"] = round(row["vllm_marlin_us"] / best, 2)
+                except Exception as e:   # a vLLM op that refuses a shape is a missing column
+                    row["vllm"] = f"{type(e).__name__}: {str(e)[:120]}"
             out.append(row)
-        del sets, base, decode
+        if name == "gate_up":
+            # awq_dequantize (the materialising op of the >= 256-token route), 2.5 B per weight
+            td = graph_time([(lambda q=q: awq_b200.awq_dequantize(q[0], q[1], q[2], 0, 0, 0))
+                             for q in sets], stream, reps=3)
+            out.append({"shape": name, "K": k, "N": n, "op": "awq_dequantize",
+                        "us": round(td * 1e6, 1), "GBps": round(2.5 * k * n / td / 1e9, 1)})
+        del sets, base, decode, kmajor, marlin
+        torch.cuda.empty_cache()
     return out
 
 
 def run_moe(dev, stream):
     """Benchmark configuration 3: Qwen3-30B-A3B fused-MoE layer (router -> permutation -> expert GEMMs ->
-    sum), T in {1 .. 4096}, 1 GPU."""
+    sum), T in {1 .. 4096}, 1 GPU; vLLM's router + fused_marlin_moe beside it."""
     import torch
     import awq_b200
     from awq_b200 import synth
+    V = _vllm_ref()
     cfg = synth.QWEN3_MOE
     e, h, i, k = cfg["experts"], cfg["hidden"], cfg["intermediate"], cfg["topk"]
-    w1, w2 = synth.moe_layer_tensors(e, h, i, GROUP)
-    w1 = tuple(a.to(dev) for a in w1)
-    w2 = tuple(a.to(dev) for a in w2)
-    d1, d2 = awq_b200.awq_repack(w1[0]), awq_b200.awq_repack(w2[0])
+    # two copies of the layer (302 MB of int4 each) alternate: more than the L2 holds
+    layers = []
+    for seed in (0, 1):
+        w1, w2 = synth.moe_layer_tensors(e, h, i, GROUP, seed=seed)
+        w1 = tuple(a.to(dev) for a in w1)
+        w2 = tuple(a.to(dev) for a in w2)
+        layers.append((w1, w2, awq_b200.awq_repack(w1[0]), awq_b200.awq_repack(w2[0]),
+                       V.marlin_moe_prepare(w1, w2) if V is not None else None))
     from awq_b200 import _lib
     block_of = lambda t: _lib.load().awq_b200_moe_block_size(t, k, e, h, i, GROUP)  # noqa: E731
+    awq_b200.reserve_workspace(awq_b200.moe_workspace_bytes(max(synth.MOE_TOKENS), k, e, h, i), dev)
     out = []
     for t in synth.MOE_TOKENS:
         x = synth.activations(t, h).to(dev)
         logits = synth.gating_logits(t, e).to(dev)
         _, ids, _ = awq_b200.fused_topk(x, logits, k, True)
         hit = int(torch.unique(ids).numel())
-        sec = graph_time([lambda: awq_b200.fused_moe(x, w1, w2, logits, k, True)], stream,
-                         reps=5 if t >= 1024 else 20)
+        reps = 5 if t >= 1024 else 20
+        with torch.cuda.stream(stream):
+            awq_b200.reserve_workspace(awq_b200.moe_workspace_bytes(max(synth.MOE_TOKENS), k, e, h, i), dev)
+        sec = graph_time([(lambda L=L: awq_b200.fused_moe(x, L[0], L[1], logits, k, True))
+                          for L in layers], stream, reps=reps)
         byts = hit * (2359296 + 73728 + 18432) + t * h * 2 * 2
         row = {"T": t, "experts_hit": hit, "us": round(sec * 1e6, 1),
                "GBps": round(byts / sec / 1e9, 1),
                "TFLOPs": round(t * 75497472 / sec / 1e12, 2)}
         if block_of(t) in (8, 16):
             # the same layer with the optional decode-layout copies of the expert weights
-            def layer():
+            def layer(L):
                 w, ids2, _ = awq_b200.fused_topk(x, logits, k, True)
-                return awq_b200.fused_experts(x, w1, w2, w, ids2, w1_decode=d1, w2_decode=d2)
-            sd = graph_time([layer], stream, reps=20)
+                return awq_b200.fused_experts(x, L[0], L[1], w, ids2, w1_decode=L[2], w2_decode=L[3])
+            sd = graph_time([(lambda L=L: layer(L)) for L in layers], stream, reps=reps)
             row["us_decode_layout"] = round(sd * 1e6, 1)
+        if V is None:
+            row["vllm"] = "compiled ops of the installed vLLM did not load"
+        else:
+            try:
+                def theirs(L):
+                    w, ids2 = V.topk_softmax(logits, k, True)
+                    return V.marlin_moe(x, L[4], w, ids2)
+                sv = graph_time([(lambda L=L: theirs(L)) for L in layers], stream,
+                                reps=max(2, reps // 2))
+                row["vllm_marlin_moe_us"] = round(sv * 1e6, 1)
+                best = min(v for kk, v in row.items() if kk.startswith("us"))
+                row["speedup_vs_vllm_marlin_moe"] = round(row["vllm_marlin_moe_us"] / best, 2)
+            except Exception as ex:
+                row["vllm"] = f"{type(ex).__name__}: {str(ex)[:120]}"
         out.append(row)
     return out
 
@@ -490,58 +656,113 @@ def run_moe(dev, stream):
 def run_tp(args, world, rank, dev, stream, barrier):
     """The same layer sharded over `world` GPUs: qkv/gate_up column-parallel, o_proj/down
     row-parallel with the fp16 [M, 8192] partial outputs all-reduced over NVLink (NCCL).  The
-    down projection's K (231 groups) is padded to a multiple of the TP degree."""
+    down projection's K (231 groups) is padded to a multiple of the TP degree.  Before timing,
+    the row-parallel results are compared with the unsharded layer computed on this GPU; the
+    step is timed both as eager launches and captured in a CUDA graph (NCCL included)."""
     import torch
     import torch.distributed as dist
+    import awq_b200
     from awq_b200 import synth, tp
 
     m = M_TOKENS
-    shards, xs = [], []
+    shards, xs, full = [], [], []
     for i, (name, (k, n)) in enumerate(shapes()):
         qw, s, qz = synth.awq_linear_tensors(k, n, GROUP, seed=i)
+        x_full = synth.activations(m, k, seed=i)
         if name in ("qkv", "gate_up"):
             sh = tp.shard_columns(qw, s, qz, rank, world)
-            x = synth.activations(m, k, seed=i)
+            x = x_full
             shards.append(("col", tuple(a.to(dev) for a in sh)))
+            full.append(None)
         else:
+            full.append((x_full.to(dev), qw.to(dev), s.to(dev), qz.to(dev)))
             qw, s, qz = tp.pad_k_for_tp(qw, s, qz, world)
             sh = tp.shard_rows(qw, s, qz, rank, world)
-            x = tp.shard_input(tp.pad_x_for_tp(synth.activations(m, k, seed=i), qw.shape[0]),
-                               rank, world)
+            x = tp.shard_input(tp.pad_x_for_tp(x_full, qw.shape[0]), rank, world)
             shards.append(("row", tuple(a.to(dev) for a in sh)))
         xs.append(x.to(dev))
 
     def step():
+        outs = []
         for (kind, sh), x in zip(shards, xs):
-            if kind == "col":
-                tp.column_parallel_forward(x, sh)
-            else:
-                tp.row_parallel_forward(x, sh)
+            outs.append(tp.column_parallel_forward(x, sh) if kind == "col"
+                        else tp.row_parallel_forward(x, sh))
+        return outs
+
+    # ---- parity: the all-reduced row-parallel outputs against the unsharded product ----
+    outs = step()
+    torch.cuda.synchronize()
+    worst = 0.0
+    for o, f in zip(outs, full):
+        if f is None:
+            continue
+        ref = awq_b200.awq_gemm(f[0], f[1], f[2], f[3], 8).float()
+        err = float((o.float() - ref).abs().max() / ref.abs().max())
+        worst = max(worst, err)
+    t = torch.tensor([worst], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    parity = float(t[0])
+    del full
+
+    def timed(fn, steps):
+        for _ in range(5):
+            fn()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]) * 1e-3 / steps
 
     steps = max(1, min(args.steps, 500))
-    for _ in range(5):
+    sec_eager = timed(step, steps)
+    sec_graph = None
+    try:
         step()
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(steps):
-        step()
-    e1.record(stream)
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    sec = float(t[0]) * 1e-3 / steps
-    return {"parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": sec * 1e3,
-            "value": weight_bytes_per_step() / sec / 1e12, "unit": UNIT, "steps": steps,
-            "collective": "nccl all_reduce fp16 [16, 8192] after o_proj and down"}
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            step()
+        sec_graph = timed(g.replay, steps)
+    except Exception as e:  # NCCL capture not possible in this configuration
+        graph_note = f"{type(e).__name__}: {str(e)[:100]}"
+    # without the collectives: what the exchange step costs
+    def step_no_ar():
+        for (kind, sh), x in zip(shards, xs):
+            tp.column_parallel_forward(x, sh)
+    sec_no_ar = None
+    try:
+        step_no_ar()
+        torch.cuda.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=stream):
+            step_no_ar()
+        sec_no_ar = timed(g2.replay, steps)
+    except Exception:
+        pass
+    sec = sec_graph if sec_graph is not None else sec_eager
+    res = {"parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": sec * 1e3,
+           "ms_per_step_eager": sec_eager * 1e3,
+           "ms_per_step_graph": None if sec_graph is None else sec_graph * 1e3,
+           "ms_per_step_graph_without_all_reduce": None if sec_no_ar is None else sec_no_ar * 1e3,
+           "value": weight_bytes_per_step() / sec / 1e12, "unit": UNIT, "steps": steps,
+           "parity_rel_err": parity,
+           "collective": "nccl all_reduce fp16 [16, 8192] after o_proj and down"}
+    if sec_graph is None:
+        res["graph_note"] = graph_note
+    return res
 
 
 def run_case(args):
     """`--case kernel:M:K:N` launches one AWQ linear of that shape `--steps` times after
     `--warmup` launches and prints its CUDA-event time: the small, bounded command the ncu
     captures under profiles/ are taken with.  kernel: auto | stream | stream_exact | stream_rp
-    (decode-layout copy of qweight) | tcgen05 | ts | wt | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
+    (decode-layout copy of qweight) | q8 (K-major copy) | tcgen05 | ts | wt | generic | dequantize | moe:T (Qwen3-30B-A3B layer with T tokens; K and N ignored)."""
     import torch
 
     import build as awq_build
@@ -572,10 +793,12 @@ def run_case(args):
             kern = {"auto": awq_b200.KERNEL_AUTO, "stream": awq_b200.KERNEL_STREAM,
                     "stream_exact": awq_b200.KERNEL_STREAM_EXACT,
                     "tcgen05": awq_b200.KERNEL_TCGEN05, "ts": awq_b200.KERNEL_TS, "wt": awq_b200.KERNEL_WT,
-                    "stream_rp": awq_b200.KERNEL_STREAM_RP,
+                    "stream_rp": awq_b200.KERNEL_STREAM_RP, "q8": awq_b200.KERNEL_Q8,
                     "generic": awq_b200.KERNEL_GENERIC}[f[0]]
             if f[0] == "stream_rp":
                 qw = awq_b200.awq_repack(qw)
+            if f[0] == "q8":
+                qw = awq_b200.awq_repack_kmajor(qw)
             fn = lambda: awq_b200.awq_gemm(x, qw, s, qz, 8, kernel=kern)  # noqa: E731
         work = f"{f[0]} M={m} K={k} N={n}"
     for _ in range(args.warmup):

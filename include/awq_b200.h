@@ -153,6 +153,14 @@ int awq_b200_device_status_clear(int* status);
 void awq_b200_set_wait_limit(unsigned int polls);
 
 /*
+ * Runs the give-up path of the bounded waits once: a one-warp kernel waits, with a limit of
+ * `polls`, on an mbarrier nobody arrives on and then on a flag nobody sets.  Both waits run out,
+ * the kernel returns normally, and awq_b200_device_status_clear then reports 90 (the first of
+ * the two).  The context stays usable.  No counterpart in the reference.
+ */
+int awq_b200_selftest_wait(unsigned int polls, void* stream);
+
+/*
  * Router: softmax over E experts, top-k (ties: lower expert id first), optional
  * renormalisation of the k weights.  gating is fp32 (gating_dtype 0) or fp16 (1), [T, E].
  * Outputs: topk_weights fp32 [T, k], topk_ids int32 [T, k], token_expert_indices int32 [T, k]

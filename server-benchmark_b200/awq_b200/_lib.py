@@ -37,6 +37,7 @@ PROTOTYPES = {
     "awq_b200_device_status": (c_int, [POINTER(c_int)]),
     "awq_b200_device_status_clear": (c_int, [POINTER(c_int)]),
     "awq_b200_set_wait_limit": (None, [c_uint]),
+    "awq_b200_selftest_wait": (c_int, [c_uint, c_void_p]),
     "awq_b200_repack_kmajor_bytes": (c_size_t, [c_int, c_int]),
     "awq_b200_repack_kmajor": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "awq_b200_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,

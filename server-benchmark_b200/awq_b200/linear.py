@@ -20,6 +20,11 @@ import torch
 from . import _lib, ops
 
 REPACK_MAX_TOKENS = 8  # the decode-layout kernel serves token counts up to this
+KMAJOR_TOKENS = (9, 16)        # token counts the K-major kernel serves (measured: below, the
+                               # streaming kernel on the decode layout is as fast or faster)
+KMAJOR_MIN_TILES_PER_SM = 64   # layer size from which the K-major kernel wins (measured on the
+                               # Qwen2.5-72B shapes: gate_up 100 tiles per SM 64 vs 83 us, down 50
+                               # tiles per SM 43 vs 40 us)
 
 
 @dataclass
@@ -30,6 +35,7 @@ class AWQConfig:
     group_size: int = 128
     zero_point: bool = True
     repack_decode: bool = False
+    decode_kmajor: bool = False
 
     def __post_init__(self) -> None:
         if self.weight_bits != 4:
@@ -46,6 +52,16 @@ class AWQConfig:
     @staticmethod
     def get_min_capability() -> int:
         return 100  # sm_100a only
+
+
+def kmajor_pays(qweight: torch.Tensor, group_size: int) -> bool:
+    """Whether the K-major decode kernel is the faster one for a layer of this size."""
+    k, words = qweight.shape
+    if group_size != 128 or k % 128 != 0 or k // 128 > 256:
+        return False
+    sms = torch.cuda.get_device_properties(qweight.device).multi_processor_count
+    tiles = -(-words * 8 // 256) * (k // 128)
+    return tiles >= KMAJOR_MIN_TILES_PER_SM * sms
 
 
 class AWQLinear(torch.nn.Module):
@@ -98,10 +114,13 @@ class AWQLinearMethod:
             p = getattr(layer, name)
             setattr(layer, name, torch.nn.Parameter(p.data.contiguous(), requires_grad=False))
         layer.qweight_decode = None
+        layer.qweight_kmajor = None
         k, words = layer.qweight.shape
         if (self.quant_config.repack_decode and layer.group_size == 128 and k % 128 == 0
                 and words % 4 == 0):
             layer.qweight_decode = ops.awq_repack(layer.qweight.data)
+        if self.quant_config.decode_kmajor and kmajor_pays(layer.qweight, layer.group_size):
+            layer.qweight_kmajor = ops.awq_repack_kmajor(layer.qweight.data)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor,
               bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -112,9 +131,14 @@ class AWQLinearMethod:
         if not reshaped_x.is_contiguous():
             reshaped_x = reshaped_x.contiguous()
         decode = getattr(layer, "qweight_decode", None)
-        if decode is not None and reshaped_x.shape[0] <= REPACK_MAX_TOKENS:
+        kmajor = getattr(layer, "qweight_kmajor", None)
+        tokens = reshaped_x.shape[0]
+        if decode is not None and tokens <= REPACK_MAX_TOKENS:
             out = ops.awq_gemm(reshaped_x, decode, scales, qzeros, pack_factor, bias=bias,
                                kernel=_lib.KERNEL_STREAM_RP)
+        elif kmajor is not None and KMAJOR_TOKENS[0] <= tokens <= KMAJOR_TOKENS[1]:
+            out = ops.awq_gemm(reshaped_x, kmajor, scales, qzeros, pack_factor, bias=bias,
+                               kernel=_lib.KERNEL_Q8)
         else:
             out = ops.awq_gemm(reshaped_x, qweight, scales, qzeros, pack_factor, bias=bias)
         return out.reshape(out_shape)

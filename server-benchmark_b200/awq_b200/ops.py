@@ -62,18 +62,49 @@ def _awq_dims(qweight, scales, qzeros, kmajor: bool = False):
 
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_retired: list[torch.Tensor] = []   # outgrown buffers: CUDA graphs captured earlier still use them
+_MIN_WORKSPACE = 8 << 20            # covers every dense kernel's scratch need
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
-    """Scratch owned by the torch caching allocator, grown on demand, one per (device, stream)."""
+    """Scratch owned by the torch caching allocator, one buffer per (device, stream).
+
+    A buffer is replaced only when a call needs more than it holds; the old one is kept alive
+    (a CUDA graph captured earlier has its address baked in).  Growing while the stream is
+    being captured would put the new buffer into the graph's private pool, so that raises:
+    size the scratch beforehand with ``reserve_workspace``."""
     if nbytes == 0:
         return None
     key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(
+                    f"the scratch buffer of this stream ({ws.numel()} bytes) would have to grow to "
+                    f"{nbytes} bytes during stream capture; call "
+                    "awq_b200.reserve_workspace(nbytes) on this stream before capturing")
+            _retired.append(ws)
+        ws = torch.empty(max(nbytes, _MIN_WORKSPACE), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def reserve_workspace(nbytes: int, device: torch.device | str | None = None) -> None:
+    """Make the current stream's scratch buffer at least ``nbytes`` large (load-time call, before
+    any CUDA-graph capture).  ``moe_workspace_bytes`` gives the need of the fused-MoE layer for a
+    token count; the dense kernels never need more than the default."""
+    dev = torch.device(device) if device is not None else torch.device("cuda",
+                                                                      torch.cuda.current_device())
+    _workspace(dev, int(nbytes))
+
+
+def moe_workspace_bytes(tokens: int, topk: int, num_experts: int, hidden: int,
+                        intermediate: int) -> int:
+    """Scratch bytes ``fused_experts`` needs for up to ``tokens`` tokens (num_experts: the global
+    expert count the routing is done over)."""
+    return int(_lib.load().awq_b200_moe_workspace_bytes(tokens, topk, num_experts, hidden,
+                                                        intermediate))
 
 
 def awq_dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,

@@ -208,6 +208,11 @@ int awq_b200_device_status_clear(int* status) { return device_status(status, 1);
 
 void awq_b200_set_wait_limit(unsigned int polls) { awq::q8_set_spin_limit(polls); }
 
+int awq_b200_selftest_wait(unsigned int polls, void* stream) {
+  if (int rc = check_device()) return rc;
+  return awq::launch_wait_selftest(polls, static_cast<cudaStream_t>(stream));
+}
+
 int awq_b200_topk_softmax(const void* gating, int gating_dtype, int T, int E, int topk,
                           int renormalize, float* topk_weights, int32_t* topk_ids,
                           int32_t* token_expert_indices, void* stream) {

@@ -194,6 +194,7 @@ int launch_gemm_q8(const __half* x, const void* qweight_km, const __half* scales
                    const uint32_t* qzeros, const __half* bias, __half* out, int M, int N, int K,
                    int group, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 void q8_set_spin_limit(uint32_t polls);
+int launch_wait_selftest(uint32_t polls, cudaStream_t stream);
 int q8_device_status(int* out, int clear);
 bool moe_wt_supported(int H, int I, int group);
 int launch_wt_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,

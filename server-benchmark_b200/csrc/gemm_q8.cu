@@ -822,6 +822,37 @@ int launch_gemm_q8(const __half* x, const void* qweight_km, const __half* scales
 
 
 
+// Exercise of the give-up path of the bounded waits: one warp waits on an mbarrier nobody arrives
+// on (the same helper every kernel uses, with a short limit), then on a flag in global memory
+// nobody sets (the wait of the stream-K finisher).  Both run out, the first one records code 90
+// in the status word, the kernel returns normally.
+__device__ int g_q8_never_set = 0;
+
+__global__ void __launch_bounds__(32) wait_selftest_kernel(uint32_t polls) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ volatile int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_n(smem_u32(&bar), 0, &s_abort, 90, polls);
+  if (threadIdx.x == 0 && !ok) {
+    uint32_t n = 0;
+    while (ld_acquire(&g_q8_never_set) == 0)
+      if (++n >= polls) {
+        atomicCAS(&g_tc_status, 0, 91);
+        break;
+      }
+  }
+}
+
+int launch_wait_selftest(uint32_t polls, cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(polls ? polls : 1);
+  return cudaGetLastError() == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
 void q8_set_spin_limit(uint32_t polls) { g_q8_spin_limit = polls ? polls : kSpinLimit; }
 
 int q8_device_status(int* out, int clear) { return read_tc_status(out, clear); }

@@ -65,16 +65,20 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA has been aborted (by this thread or another).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
+__device__ __forceinline__ bool mbar_wait_n(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int code, uint32_t limit) {
   if (mbar_try_wait(bar, parity)) return true;  // fast path: the phase is already complete
-  for (uint32_t i = 1; i < kSpinLimit; ++i) {
+  for (uint32_t i = 1; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 31u) == 0 && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(&g_tc_status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  return mbar_wait_n(bar, parity, abort_flag, code, kSpinLimit);
 }
 // True in exactly one lane of a fully active warp (always the same lane).  A tcgen05.mma or
 // tcgen05.commit issued this way from a converged warp costs its warp ~25-45 cycles; issued from

@@ -156,3 +156,19 @@ def test_q8_rejects_what_it_cannot_take(A):
     rc = lib.awq_b200_gemm(x.data_ptr(), km.data_ptr(), s.data_ptr(), qz.data_ptr(), None,
                            out.data_ptr(), 1, 256, 256, 128, A.KERNEL_Q8, ws.data_ptr(), 1024, None)
     assert rc == -5
+
+
+def test_bounded_waits_give_up_and_the_context_survives(A):
+    """A wait that nothing satisfies runs out after its limit, records its code in the status
+    word and lets the kernel return; the status word is sticky until cleared; afterwards the
+    GPU context is still usable."""
+    from awq_b200 import synth, _lib
+    lib = _lib.load()
+    assert device_status() == 0
+    assert lib.awq_b200_selftest_wait(2000, None) == 0
+    torch.cuda.synchronize()
+    assert device_status(clear=False) == 90       # the mbarrier wait gave up first
+    assert device_status(clear=False) == 90       # sticky
+    assert device_status(clear=True) == 90
+    assert device_status() == 0                   # cleared
+    run_case(A, 16, 1024, 512, seed=2, check_pack=False)
