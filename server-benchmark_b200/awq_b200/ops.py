@@ -280,10 +280,15 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
                   apply_router_weight_on_input: bool = False, global_num_experts: int = -1,
                   expert_map: torch.Tensor | None = None, group_size: int = 128,
                   w1_decode: torch.Tensor | None = None,
-                  w2_decode: torch.Tensor | None = None) -> torch.Tensor:
+                  w2_decode: torch.Tensor | None = None, quant_config=None) -> torch.Tensor:
     """AWQ fused-MoE experts.  ``w1`` and ``w2`` are (qweight, scales, qzeros) triples of the
     stacked AWQ tensors: w1 = (i32 [E,H,2I/8], f16 [E,H/G,2I], i32 [E,H/G,2I/8]),
     w2 = (i32 [E,I,H/8], f16 [E,I/G,H], i32 [E,I/G,H/8]).  Returns fp16 [T, H].
+
+    The form of vLLM's ``fused_experts`` (fused_moe/fused_moe.py:1587-1599) is accepted too:
+    ``w1`` / ``w2`` the two stacked qweight tensors and ``quant_config`` an object carrying
+    ``w1_scale``, ``w2_scale``, ``w1_zp``, ``w2_zp`` (a ``FusedMoEQuantConfig``, e.g. from
+    ``int4_w4a16_moe_quant_config``); its ``block_shape[1]``, when set, is the group size.
 
     ``w1_decode`` / ``w2_decode`` (both or neither): ``awq_repack`` of the two stacked qweights,
     made once at load time.  Batches small enough for the weight-streaming expert kernels
@@ -293,6 +298,19 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
         raise ValueError("only the silu activation is implemented")
     if apply_router_weight_on_input:
         raise ValueError("apply_router_weight_on_input is not implemented")
+    if quant_config is not None:
+        if not (torch.is_tensor(w1) and torch.is_tensor(w2)):
+            raise ValueError("with quant_config, w1 and w2 are the stacked qweight tensors")
+        w1 = (w1, quant_config.w1_scale, quant_config.w1_zp)
+        w2 = (w2, quant_config.w2_scale, quant_config.w2_zp)
+        if w1[1] is None or w1[2] is None or w2[1] is None or w2[2] is None:
+            raise ValueError("quant_config must carry w1_scale, w2_scale, w1_zp and w2_zp")
+        shape = getattr(quant_config, "block_shape", None)
+        if shape is not None and len(shape) == 2 and shape[1]:
+            group_size = int(shape[1])
+    elif torch.is_tensor(w1) or torch.is_tensor(w2):
+        raise ValueError("w1 and w2 are (qweight, scales, qzeros) triples, or tensors together "
+                         "with quant_config")
     w13_q, w13_s, w13_z = w1
     w2_q, w2_s, w2_z = w2
     _require(hidden_states, "hidden_states", torch.float16, 2)

@@ -135,6 +135,28 @@ def test_fused_experts_vs_oracle(A, e, h, i, t, k):
     assert O.rel_err(y2, ref) < TOL
 
 
+def test_fused_experts_accepts_the_reference_call_form(A):
+    """w1 / w2 as the stacked qweight tensors plus a quant_config object carrying scales and zero
+    points (vLLM fused_moe.py:1587-1599) gives the same bits as the triple form."""
+    from types import SimpleNamespace
+    e, h, i, t, k = 16, 512, 256, 33, 4
+    w1, w2, x, logits = _moe_case(e, h, i, t, k, seed=5)
+    w1d = tuple(a.cuda() for a in w1)
+    w2d = tuple(a.cuda() for a in w2)
+    wts, ids, _ = A.fused_topk(x.cuda(), logits.cuda(), k, True)
+    y = A.fused_experts(x.cuda(), w1d, w2d, wts, ids)
+    qc = SimpleNamespace(w1_scale=w1d[1], w2_scale=w2d[1], w1_zp=w1d[2], w2_zp=w2d[2],
+                         block_shape=[0, 128])
+    y2 = A.fused_experts(x.cuda(), w1d[0], w2d[0], wts, ids, quant_config=qc)
+    assert torch.equal(y, y2)
+    with pytest.raises(ValueError):
+        A.fused_experts(x.cuda(), w1d[0], w2d[0], wts, ids)
+    with pytest.raises(ValueError):
+        A.fused_experts(x.cuda(), w1d[0], w2d[0], wts, ids,
+                        quant_config=SimpleNamespace(w1_scale=w1d[1], w2_scale=w2d[1],
+                                                     w1_zp=None, w2_zp=None))
+
+
 @pytest.mark.parametrize("t", [20, 400])
 def test_fused_experts_expert_parallel_shards_sum(A, t):
     """Two expert-parallel shards (expert_map) add up to the unsharded layer (T = 20: streaming

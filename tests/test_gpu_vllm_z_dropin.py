@@ -54,45 +54,42 @@ def test_vllm_awq_linear_method_runs_on_our_ops(built_library):
     assert y.shape == (4, n)
 
 
-def test_vllm_linear_method_with_decode_copy(built_library):
-    """register(repack_decode=True): vLLM's own AWQLinearMethod keeps the decode-layout copy after
-    loading and serves small batches from it."""
+def test_plugin_linear_method_with_layout_copies(built_library):
+    """register(repack_decode=True, decode_kmajor=True): the plug-in's linear method keeps the
+    decode-layout copy (and, for layers large enough, the K-major copy) after loading and serves
+    each token count from the layout made for it."""
     try:
         import vllm._C  # noqa: F401
         from vllm.model_executor.layers.quantization import awq as vllm_awq
     except Exception as e:  # pragma: no cover
         pytest.skip(f"vllm not usable here: {e}")
     from awq_b200 import synth, vllm_plugin
-    saved = (vllm_awq.AWQLinearMethod.apply,
-             vllm_awq.AWQLinearMethod.process_weights_after_loading)
+    vllm_plugin.register(repack_decode=True, decode_kmajor=True)
     try:
-        vllm_plugin.register(repack_decode=True)
-        vllm_plugin.register(repack_decode=True)   # idempotent
-        k, n = 2048, 1536
-        qw, s, qz = synth.awq_linear_tensors(k, n, 128, seed=43)
-        try:
-            cfg = vllm_awq.AWQConfig(weight_bits=4, group_size=128, zero_point=True)
-        except TypeError:
-            cfg = vllm_awq.AWQConfig(4, 128, True)
-        method = vllm_awq.AWQLinearMethod(cfg)
+        method_cls = vllm_plugin.classes["linear"]
+        assert issubclass(method_cls, vllm_awq.AWQLinearMethod)
+        cfg = vllm_awq.AWQConfig(weight_bits=4, group_size=128, zero_point=True)
+        for (k, n, want_kmajor) in ((2048, 1536, False), (8192, 29568, True)):
+            qw, s, qz = synth.awq_linear_tensors(k, n, 128, seed=43)
+            method = method_cls(cfg)
 
-        class Layer(torch.nn.Module):
-            pass
+            class Layer(torch.nn.Module):
+                pass
 
-        layer = Layer()
-        layer.qweight = torch.nn.Parameter(qw.cuda(), requires_grad=False)
-        layer.scales = torch.nn.Parameter(s.cuda(), requires_grad=False)
-        layer.qzeros = torch.nn.Parameter(qz.cuda(), requires_grad=False)
-        method.process_weights_after_loading(layer)
-        assert layer.qweight_decode is not None
-        assert layer.qweight_decode.shape == layer.qweight.shape
-        for m in (1, 8, 9, 300):
-            x = synth.activations(m, k, seed=m).cuda()
-            y = method.apply(layer, x)
-            assert y.shape == (m, n) and y.dtype == torch.float16
-            ref = O.awq_gemm_fp32(x.cpu().numpy(), qw.numpy(), s.numpy(), qz.numpy(), 128)
-            assert O.rel_err(y.float().cpu().numpy(), ref) < 1e-2
+            layer = Layer()
+            layer.qweight = torch.nn.Parameter(qw.cuda(), requires_grad=False)
+            layer.scales = torch.nn.Parameter(s.cuda(), requires_grad=False)
+            layer.qzeros = torch.nn.Parameter(qz.cuda(), requires_grad=False)
+            method.process_weights_after_loading(layer)
+            assert layer.qweight_decode is not None
+            assert layer.qweight_decode.shape == layer.qweight.shape
+            assert (layer.qweight_kmajor is not None) == want_kmajor
+            w = O.dequantize_fp32(qw.numpy(), s.numpy(), qz.numpy(), 128)
+            for m in (1, 8, 9, 16, 300):
+                x = synth.activations(m, k, seed=m).cuda()
+                y = method.apply(layer, x)
+                assert y.shape == (m, n) and y.dtype == torch.float16
+                ref = x.cpu().numpy().astype(np.float32) @ w
+                assert O.rel_err(y.float().cpu().numpy(), ref) < 1e-2
     finally:
-        (vllm_awq.AWQLinearMethod.apply,
-         vllm_awq.AWQLinearMethod.process_weights_after_loading) = saved
-        vllm_awq.AWQLinearMethod._awq_b200_repack = False
+        vllm_plugin.register()   # options back to the defaults
