@@ -69,7 +69,7 @@ def test_plugin_linear_method_with_layout_copies(built_library):
         method_cls = vllm_plugin.classes["linear"]
         assert issubclass(method_cls, vllm_awq.AWQLinearMethod)
         cfg = vllm_awq.AWQConfig(weight_bits=4, group_size=128, zero_point=True)
-        for (k, n, want_kmajor) in ((2048, 1536, False), (8192, 29568, True)):
+        for (k, n, want_kmajor) in ((2048, 1536, False), (8192, 59136, True)):
             qw, s, qz = synth.awq_linear_tensors(k, n, 128, seed=43)
             method = method_cls(cfg)
 

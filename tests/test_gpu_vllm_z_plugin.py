@@ -107,7 +107,8 @@ def test_vllm_linear_layers_run_our_kernels(env):
         for m in (1, 16, 300):
             x = synth.activations(m, k, seed=m)
             before = vllm_plugin.calls["linear"]
-            y = layer(x.cuda())
+            with torch.inference_mode():
+                y = layer(x.cuda())
             y = y[0] if isinstance(y, tuple) else y
             assert vllm_plugin.calls["linear"] == before + 1
             assert y.shape == (m, n) and y.dtype == torch.float16
