@@ -1,0 +1,166 @@
+"""One serving measurement from start to finish, the job of the reference's
+benchmarks/3_vllm_benchmark.sh on one box without containers:
+
+  1. write the random-init model directory (model_dir),
+  2. start N vLLM servers on contiguous GPU slices (replicas) and, for N > 1, the front,
+  3. wait for the health check, run ``vllm bench serve`` with the reference's flags (client),
+  4. write ``<results>/<gpu>_x_<count>_<model>_vllm_benchmark.txt`` in the reference's layout and
+     print one JSON line with the parsed figures; a result file that exists is not re-run
+     (run_remote_benchmark.py:186-195,307-310) unless --force.
+
+    python -m awq_b200.serving.run --arch qwen3-30b-a3b --instances 8 --concurrency 256 \
+        --num-prompts 1024 --plugin on
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shlex
+import socket
+import subprocess
+import sys
+import tempfile
+import time
+
+from . import client, model_dir, replicas
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def topology_text(args, ports: list[int], cmds: list[list[str]], envs: list[dict]) -> str:
+    """What the compose file says in the reference: one entry per instance with its GPUs, port
+    and command, then the front."""
+    lines = ["services:"]
+    for i, (port, cmd, env) in enumerate(zip(ports, cmds, envs)):
+        lines += [f"  vllm_{i}:",
+                  f"    device_ids: [{', '.join(repr(g) for g in env['CUDA_VISIBLE_DEVICES'].split(','))}]",
+                  f"    port: {port}",
+                  f"    plugin: {args.plugin}",
+                  f"    command: {' '.join(shlex.quote(c) for c in cmd[3:])}"]
+    if len(ports) > 1:
+        lines += ["  front:", f"    policy: {args.policy}",
+                  "    backends: [" + ", ".join(f"vllm_{i}" for i in range(len(ports))) + "]"]
+    return "\n".join(lines)
+
+
+def run(args) -> dict:
+    served = args.model_name
+    gpus = args.instances * args.tensor_parallel_size * args.pipeline_parallel_size
+    server_name = f"{args.gpu_name}_x_{gpus}"
+    os.makedirs(args.results_dir, exist_ok=True)
+    suffix = "" if args.plugin == "on" else f"-stock-{args.plugin}"
+    out_path = os.path.join(args.results_dir,
+                            client.result_file_name(server_name, served + suffix + args.tag))
+    if os.path.exists(out_path) and not args.force:
+        with open(out_path) as f:
+            parsed = client.parse_result_block(f.read())
+        return {"result_file": out_path, "skipped": "result exists", **parsed}
+
+    work = args.work_dir or tempfile.mkdtemp(prefix="awq_b200_serving_")
+    mdir = model_dir.write_model_dir(os.path.join(work, "model"), args.arch,
+                                     num_layers=args.num_layers)
+    group = replicas.Replicas()
+    front = None
+    t0 = time.time()
+    try:
+        ports, cmds, envs = [], [], []
+        per = args.tensor_parallel_size * args.pipeline_parallel_size
+        for i in range(args.instances):
+            port = _free_port()
+            cmd = replicas.serve_command(mdir, served, port, args.tensor_parallel_size,
+                                         args.pipeline_parallel_size, args.extra_args)
+            env = replicas.replica_env(i, per, args.plugin, args.seed, {
+                "AWQ_B200_REPACK_DECODE": int(args.repack_decode),
+                "AWQ_B200_DECODE_KMAJOR": int(args.decode_kmajor)})
+            group.launch(cmd, env, port, os.path.join(work, f"vllm_{i}.log"))
+            ports.append(port), cmds.append(cmd), envs.append(env)
+        group.wait_ready(args.startup_timeout)
+        startup_s = time.time() - t0
+        if args.instances > 1:
+            fport = _free_port()
+            fcmd = [sys.executable, "-m", "awq_b200.serving.front", "--port", str(fport),
+                    "--policy", args.policy]
+            for p in ports:
+                fcmd += ["--backend", f"http://127.0.0.1:{p}"]
+            fenv = dict(os.environ, PYTHONPATH=replicas.PACKAGE_PARENT + os.pathsep +
+                        os.environ.get("PYTHONPATH", ""))
+            front = subprocess.Popen(fcmd, env=fenv, start_new_session=True)
+            base = f"http://127.0.0.1:{fport}"
+            time.sleep(2.0)
+        else:
+            base = f"http://127.0.0.1:{ports[0]}"
+        bcmd = client.benchmark_command(served, base, args.random_input_len,
+                                        args.random_output_len, args.concurrency,
+                                        args.num_prompts, tokenizer=mdir)
+        benv = dict(os.environ, CUDA_VISIBLE_DEVICES="", HF_HUB_OFFLINE="1",
+                    TRANSFORMERS_OFFLINE="1")
+        t1 = time.time()
+        res = subprocess.run(bcmd, env=benv, capture_output=True, text=True,
+                             timeout=args.client_timeout)
+        client_s = time.time() - t1
+        if res.returncode != 0:
+            raise RuntimeError("benchmark client failed:\n" + (res.stdout + res.stderr)[-4000:])
+        block = client.legacy_result_block(
+            res.stdout, topology_text(args, ports, cmds, envs),
+            " ".join(shlex.quote(c) for c in bcmd[3:]))
+        with open(out_path, "w") as f:
+            f.write(block)
+        parsed = client.parse_result_block(block)
+        return {"result_file": out_path, "server": server_name, "model": served,
+                "plugin": args.plugin, "instances": args.instances,
+                "concurrency": args.concurrency, "num_prompts": args.num_prompts,
+                "startup_s": round(startup_s, 1), "client_s": round(client_s, 1), **parsed}
+    except Exception:
+        for i, log in enumerate(group.logs):
+            try:
+                with open(log) as f:
+                    tail = f.read()[-6000:]
+                sys.stderr.write(f"---- vllm_{i} log tail ----\n{tail}\n")
+            except OSError:
+                pass
+        raise
+    finally:
+        if front is not None and front.poll() is None:
+            front.terminate()
+        group.stop()
+
+
+def parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--arch", default="qwen3-30b-a3b", choices=sorted(model_dir.ARCHITECTURES))
+    ap.add_argument("--model-name", default="synthetic/Qwen3-30B-A3B-AWQ-random")
+    ap.add_argument("--num-layers", type=int, default=None)
+    ap.add_argument("--instances", type=int, default=1)
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--pipeline-parallel-size", type=int, default=1)
+    ap.add_argument("--extra-args", default="--max-model-len 8192")
+    ap.add_argument("--plugin", default="on", choices=["on", "fill", "off"])
+    ap.add_argument("--repack-decode", action="store_true")
+    ap.add_argument("--decode-kmajor", action="store_true")
+    ap.add_argument("--policy", default="round_robin", choices=["round_robin", "least_conn"])
+    ap.add_argument("--concurrency", type=int, default=1)
+    ap.add_argument("--num-prompts", type=int, default=100)
+    ap.add_argument("--random-input-len", type=int, default=1000)
+    ap.add_argument("--random-output-len", type=int, default=1000)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--gpu-name", default="b200")
+    ap.add_argument("--results-dir", default="results")
+    ap.add_argument("--tag", default="", help="appended to the model part of the file name")
+    ap.add_argument("--work-dir", default=None)
+    ap.add_argument("--startup-timeout", type=float, default=1800.0)
+    ap.add_argument("--client-timeout", type=float, default=3600.0)
+    ap.add_argument("--force", action="store_true")
+    return ap
+
+
+def main() -> None:
+    print(json.dumps(run(parser().parse_args())), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -30,6 +30,8 @@ what a vLLM that loads the plug-in itself sees):
                  parameters uninitialised (model_loader/weight_utils.py:1484-1490) and draws
                  float ones from +-1e-3, not the nibble-uniform / scale-uniform[0.002, 0.02]
                  distributions of the benchmark.
+  mode           [AWQ_B200_MODE=kernels|fill_only]  fill_only leaves vLLM's own methods in place
+                 and only applies the seeded fill before them (the stock column of a comparison)
 ``calls`` counts how often each method ran (for tests that must see these kernels, not vLLM's).
 """
 from __future__ import annotations
@@ -237,11 +239,47 @@ def _build_methods():
 classes: dict = {}
 
 
+def _install_fill_only() -> None:
+    """Stock vLLM methods, same weights: the seeded fill runs before vLLM's own
+    ``process_weights_after_loading`` (Marlin repack included), nothing else changes.  This is
+    the stock column of the serving comparison."""
+    from vllm.model_executor.layers.quantization.awq import AWQLinearMethod
+    from vllm.model_executor.layers.quantization.awq_marlin import (AWQMarlinLinearMethod,
+                                                                    AWQMarlinMoEMethod)
+
+    def wrap_linear(cls):
+        stock = cls.process_weights_after_loading
+
+        def process(self, layer):
+            if _options["dummy_fill"] is not None:
+                fill_awq_tensors(layer.qweight.data, layer.scales.data, layer.qzeros.data,
+                                 _options["dummy_fill"] + _name_seed(layer))
+            return stock(self, layer)
+
+        cls.process_weights_after_loading = process
+
+    wrap_linear(AWQLinearMethod)
+    wrap_linear(AWQMarlinLinearMethod)
+    stock_moe = AWQMarlinMoEMethod.process_weights_after_loading
+
+    def process_moe(self, layer):
+        if _options["dummy_fill"] is not None:
+            seed = _options["dummy_fill"] + _name_seed(layer)
+            fill_awq_tensors(layer.w13_qweight.data, layer.w13_scales.data,
+                             layer.w13_qzeros.data, seed + 1)
+            fill_awq_tensors(layer.w2_qweight.data, layer.w2_scales.data,
+                             layer.w2_qzeros.data, seed + 2)
+        return stock_moe(self, layer)
+
+    AWQMarlinMoEMethod.process_weights_after_loading = process_moe
+
+
 def register(full_gemm: bool = True, repack_decode: bool = False, decode_kmajor: bool = False,
-             dummy_fill: int | None = None) -> None:
-    """Install both hooks.  Needs vLLM's compiled ops to be importable (the op schemas are defined
-    by vllm._C).  ``full_gemm`` is kept for callers of the earlier signature: the linear method
-    always uses the fused kernels for every token count now."""
+             dummy_fill: int | None = None, mode: str | None = None) -> None:
+    """Install the hooks.  Needs vLLM's compiled ops to be importable (the op schemas are defined
+    by vllm._C).  ``mode`` [AWQ_B200_MODE]: "kernels" (default: both hooks of the module text) or
+    "fill_only" (stock vLLM kernels on the seeded weights).  ``full_gemm`` is kept for callers of
+    the earlier signature: the linear method uses the fused kernels for every token count."""
     global _registered, _lib_handle
     env = os.environ.get
     _options["repack_decode"] = repack_decode or env("AWQ_B200_REPACK_DECODE") == "1"
@@ -251,6 +289,13 @@ def register(full_gemm: bool = True, repack_decode: bool = False, decode_kmajor:
     _options["dummy_fill"] = dummy_fill
     if _registered:
         return
+    mode = mode or env("AWQ_B200_MODE") or "kernels"
+    if mode == "fill_only":
+        _install_fill_only()
+        _registered = True
+        return
+    if mode != "kernels":
+        raise ValueError("mode is 'kernels' or 'fill_only'")
     import vllm._C  # noqa: F401  (defines the _C op schemas)
     lib = torch.library.Library("_C", "IMPL")
     lib.impl("awq_gemm", _awq_gemm, "CUDA", allow_override=True)
