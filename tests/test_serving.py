@@ -239,3 +239,19 @@ def test_topology_text_lists_slices(tmp_path):
     assert "device_ids: ['0', '1']" in text and "device_ids: ['2', '3']" in text
     assert "front:" in text and "policy: round_robin" in text
     assert serving.replica_gpu_list(1, 2) == "2,3"
+
+
+def test_plugin_classes_pickle_by_reference():
+    """vLLM pickles its config, quantization config object included, for every engine process it
+    spawns: the plug-in's classes must be importable by name."""
+    import pickle
+    try:
+        from awq_b200 import vllm_methods
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"vllm layer modules do not import here: {e}")
+    for cls in (vllm_methods.B200AWQConfig, vllm_methods.B200AWQMarlinConfig,
+                vllm_methods.B200AWQLinearMethod, vllm_methods.B200AWQMoEMethod):
+        assert pickle.loads(pickle.dumps(cls)) is cls
+    cfg = vllm_methods.B200AWQConfig(4, 128, True)
+    back = pickle.loads(pickle.dumps(cfg))
+    assert type(back) is vllm_methods.B200AWQConfig and back.group_size == 128
