@@ -8,8 +8,8 @@ benchmarks/3_vllm_benchmark.sh on one box without containers:
      print one JSON line with the parsed figures; a result file that exists is not re-run
      (run_remote_benchmark.py:186-195,307-310) unless --force.
 
-    python -m awq_b200.serving.run --arch qwen3-30b-a3b --instances 8 --concurrency 256 \
-        --num-prompts 1024 --plugin on
+    python -m awq_b200.serving.run --arch qwen3-30b-a3b --instances 8 \
+        --concurrency 1,16,64,256 --num-prompts 8,64,256,1024 --plugin on
 """
 from __future__ import annotations
 
@@ -48,18 +48,43 @@ def topology_text(args, ports: list[int], cmds: list[list[str]], envs: list[dict
     return "\n".join(lines)
 
 
+def _pairs(args) -> list[tuple[int, int]]:
+    """(concurrency, prompts) of every client run against one set of servers."""
+    conc = [int(c) for c in str(args.concurrency).split(",")]
+    prompts = [int(n) for n in str(args.num_prompts).split(",")]
+    if len(prompts) == 1:
+        prompts = prompts * len(conc)
+    if len(prompts) != len(conc):
+        raise ValueError("--num-prompts has one value or one per --concurrency value")
+    return list(zip(conc, prompts))
+
+
 def run(args) -> dict:
     served = args.model_name
     gpus = args.instances * args.tensor_parallel_size * args.pipeline_parallel_size
     server_name = f"{args.gpu_name}_x_{gpus}"
     os.makedirs(args.results_dir, exist_ok=True)
     suffix = "" if args.plugin == "on" else f"-stock-{args.plugin}"
-    out_path = os.path.join(args.results_dir,
-                            client.result_file_name(server_name, served + suffix + args.tag))
-    if os.path.exists(out_path) and not args.force:
-        with open(out_path) as f:
-            parsed = client.parse_result_block(f.read())
-        return {"result_file": out_path, "skipped": "result exists", **parsed}
+    pairs = _pairs(args)
+
+    def out_path(conc: int) -> str:
+        tag = args.tag + (f"-c{conc}" if len(pairs) > 1 else "")
+        return os.path.join(args.results_dir,
+                            client.result_file_name(server_name, served + suffix + tag))
+
+    runs, todo = [], []
+    for conc, prompts in pairs:
+        path = out_path(conc)
+        if os.path.exists(path) and not args.force:
+            with open(path) as f:
+                runs.append({"result_file": path, "skipped": "result exists",
+                             "concurrency": conc, **client.parse_result_block(f.read())})
+        else:
+            todo.append((conc, prompts))
+    summary = {"server": server_name, "model": served, "plugin": args.plugin,
+               "instances": args.instances, "runs": runs}
+    if not todo:
+        return summary
 
     work = args.work_dir or tempfile.mkdtemp(prefix="awq_b200_serving_")
     mdir = model_dir.write_model_dir(os.path.join(work, "model"), args.arch,
@@ -80,7 +105,7 @@ def run(args) -> dict:
             group.launch(cmd, env, port, os.path.join(work, f"vllm_{i}.log"))
             ports.append(port), cmds.append(cmd), envs.append(env)
         group.wait_ready(args.startup_timeout)
-        startup_s = time.time() - t0
+        summary["startup_s"] = round(time.time() - t0, 1)
         if args.instances > 1:
             fport = _free_port()
             fcmd = [sys.executable, "-m", "awq_b200.serving.front", "--port", str(fport),
@@ -94,27 +119,28 @@ def run(args) -> dict:
             time.sleep(2.0)
         else:
             base = f"http://127.0.0.1:{ports[0]}"
-        bcmd = client.benchmark_command(served, base, args.random_input_len,
-                                        args.random_output_len, args.concurrency,
-                                        args.num_prompts, tokenizer=mdir)
         benv = dict(os.environ, CUDA_VISIBLE_DEVICES="", HF_HUB_OFFLINE="1",
                     TRANSFORMERS_OFFLINE="1")
-        t1 = time.time()
-        res = subprocess.run(bcmd, env=benv, capture_output=True, text=True,
-                             timeout=args.client_timeout)
-        client_s = time.time() - t1
-        if res.returncode != 0:
-            raise RuntimeError("benchmark client failed:\n" + (res.stdout + res.stderr)[-4000:])
-        block = client.legacy_result_block(
-            res.stdout, topology_text(args, ports, cmds, envs),
-            " ".join(shlex.quote(c) for c in bcmd[3:]))
-        with open(out_path, "w") as f:
-            f.write(block)
-        parsed = client.parse_result_block(block)
-        return {"result_file": out_path, "server": server_name, "model": served,
-                "plugin": args.plugin, "instances": args.instances,
-                "concurrency": args.concurrency, "num_prompts": args.num_prompts,
-                "startup_s": round(startup_s, 1), "client_s": round(client_s, 1), **parsed}
+        for conc, prompts in todo:
+            bcmd = client.benchmark_command(served, base, args.random_input_len,
+                                            args.random_output_len, conc, prompts,
+                                            tokenizer=mdir)
+            t1 = time.time()
+            res = subprocess.run(bcmd, env=benv, capture_output=True, text=True,
+                                 timeout=args.client_timeout)
+            if res.returncode != 0:
+                raise RuntimeError("benchmark client failed:\n" +
+                                   (res.stdout + res.stderr)[-4000:])
+            block = client.legacy_result_block(
+                res.stdout, topology_text(args, ports, cmds, envs),
+                " ".join(shlex.quote(c) for c in bcmd[3:]))
+            path = out_path(conc)
+            with open(path, "w") as f:
+                f.write(block)
+            runs.append({"result_file": path, "concurrency": conc, "num_prompts": prompts,
+                         "client_s": round(time.time() - t1, 1),
+                         **client.parse_result_block(block)})
+        return summary
     except Exception:
         for i, log in enumerate(group.logs):
             try:
@@ -143,8 +169,8 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--repack-decode", action="store_true")
     ap.add_argument("--decode-kmajor", action="store_true")
     ap.add_argument("--policy", default="round_robin", choices=["round_robin", "least_conn"])
-    ap.add_argument("--concurrency", type=int, default=1)
-    ap.add_argument("--num-prompts", type=int, default=100)
+    ap.add_argument("--concurrency", default="1", help="one value or a comma-separated list")
+    ap.add_argument("--num-prompts", default="100", help="one value, or one per concurrency")
     ap.add_argument("--random-input-len", type=int, default=1000)
     ap.add_argument("--random-output-len", type=int, default=1000)
     ap.add_argument("--seed", type=int, default=0)

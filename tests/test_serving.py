@@ -228,7 +228,12 @@ def test_existing_result_is_not_rerun(tmp_path):
     name = client.result_file_name("b200_x_8", args.model_name)
     (tmp_path / name).write_text(client.legacy_result_block(CLIENT_OUTPUT, "services:", "cmd"))
     out = run.run(args)                            # no server is started: the file is there
-    assert out["skipped"] == "result exists" and out["total_token_throughput"] == 4096.0
+    assert len(out["runs"]) == 1
+    assert out["runs"][0]["skipped"] == "result exists"
+    assert out["runs"][0]["total_token_throughput"] == 4096.0
+    many = run.parser().parse_args(["--concurrency", "1,16", "--num-prompts", "8,64"])
+    assert run._pairs(many) == [(1, 8), (16, 64)]
+    assert run._pairs(run.parser().parse_args(["--concurrency", "1,16"])) == [(1, 100), (16, 100)]
 
 
 def test_topology_text_lists_slices(tmp_path):
