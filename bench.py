@@ -479,6 +479,7 @@ def run_cuda(args):
                                        "point": {"shape": big["shape"], "M": big["M"]}}
             line["sweep"] = sweep
             line["moe"] = moe
+        line["serving"] = recorded_serving()
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -758,6 +759,51 @@ def run_tp(args, world, rank, dev, stream, barrier):
     return res
 
 
+def recorded_serving():
+    """The serving result files committed under profiles/serving (written by
+    ``python -m awq_b200.serving.run`` in the reference's result layout), parsed with the
+    reference report's labels.  They are recordings of earlier runs on B200 boxes of this pool,
+    not measurements of this invocation: ``bench.py --serving`` measures live."""
+    import glob
+    import re
+    from awq_b200.serving import client
+    runs = []
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "serving", "*_vllm_benchmark.txt"))):
+        name = os.path.basename(path)
+        mt = re.match(r"(b200_x_(\d+))_(.+?)(-stock-(fill|off))?-c(\d+)_vllm_benchmark\.txt", name)
+        if not mt:
+            continue
+        with open(path) as f:
+            parsed = client.parse_result_block(f.read())
+        if parsed:
+            runs.append({"file": "profiles/serving/" + name, "gpus": int(mt.group(2)),
+                         "kernels": "stock vLLM (Marlin), same seeded weights" if mt.group(4)
+                         else "this package (plug-in)",
+                         "concurrency": int(mt.group(6)), **parsed})
+    return {"source": "recorded result files (not measured by this invocation)",
+            "workload": "Qwen3-30B-A3B architecture, random-init AWQ, 1000 in / 1000 out, "
+                        "vllm bench serve on /v1/chat/completions, TP=1 replicas",
+            "runs": runs}
+
+
+def run_serving(args):
+    """Live serving measurement on ``--gpus`` replicas (no torchrun: the servers own the GPUs)."""
+    from awq_b200.serving import run as srun
+    sargs = srun.parser().parse_args([
+        "--instances", str(args.gpus), "--concurrency", args.serving_concurrency,
+        "--num-prompts", args.serving_prompts, "--plugin", args.serving_plugin,
+        "--results-dir", os.path.join(ROOT, "results"), "--force"])
+    out = srun.run(sargs)
+    best = max(out["runs"], key=lambda r: r.get("output_throughput", 0.0))
+    print(json.dumps({"metric": "decode output tok/s per box", "value": best["output_throughput"],
+                      "unit": "tok/s", "n_gpus": args.gpus, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "qwen3-30b-a3b random-init AWQ, 1000 in / 1000 out, "
+                                             f"concurrency {best['concurrency']}",
+                                 "parallelism": f"replicas x{args.gpus}"},
+                      "serving": out}))
+
+
 def run_case(args):
     """`--case kernel:M:K:N` launches one AWQ linear of that shape `--steps` times after
     `--warmup` launches and prints its CUDA-event time: the small, bounded command the ncu
@@ -824,8 +870,16 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the shape sweep and the MoE layer (extra keys of the 1-GPU line)")
+    ap.add_argument("--serving", action="store_true",
+                    help="serve the random-init Qwen3-30B-A3B model on --gpus replicas and run the "
+                         "OpenAI-endpoint client (minutes; run without torchrun)")
+    ap.add_argument("--serving-concurrency", default="64,256")
+    ap.add_argument("--serving-prompts", default="256,1024")
+    ap.add_argument("--serving-plugin", default="on", choices=["on", "fill", "off"])
     args = ap.parse_args()
-    if args.case:
+    if args.serving:
+        run_serving(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)
