@@ -125,6 +125,19 @@ size_t awq_b200_repack_kmajor_bytes(int K, int N);
 
 int awq_b200_repack_kmajor(const void* qweight, void* out, int K, int N, void* stream);
 
+/*
+ * Load-time conversion of stacked expert weights from the byte layout of vLLM's MoE WNA16 method
+ * to the AWQ checkpoint layout the expert entry points below take.  In: w uint8 [E, N, K/2]
+ * (k = 2j in the low nibble of byte j), scales fp16 [E, N, K/group], zeros uint8 [E, N/2, K/group]
+ * (n = 2i in the low nibble of row i) -- the parameters MoeWNA16Method.create_weights declares
+ * (quantization/moe_wna16.py:252-324).  Out: qweight int32 [E, K, N/8] and qzeros int32
+ * [E, K/group, N/8] in AWQ nibble order, scales fp16 [E, K/group, N].  Bit-exact inverse of the
+ * converter in that method's weight loader (moe_wna16.py:389-425).  N % 8 == 0, K % group == 0.
+ */
+int awq_b200_wna16_to_awq(const void* w, const void* scales, const void* zeros, void* qweight,
+                          void* scales_out, void* qzeros, int E, int N, int K, int group,
+                          void* stream);
+
 int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const void* qzeros,
                   const void* bias, void* out, int M, int N, int K, int group, int kernel,
                   void* workspace, size_t workspace_bytes, void* stream);

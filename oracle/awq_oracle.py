@@ -140,6 +140,43 @@ def pack_kmajor(qweight, group: int = 128) -> np.ndarray:
     return np.ascontiguousarray((t[..., 0::2] | (t[..., 1::2] << 4)).astype(np.uint8)).reshape(-1)
 
 
+def awq_to_wna16_qweight(qweight) -> np.ndarray:
+    """AWQ qweight int32 [K, N/8] -> the "standard" layout of vLLM's MoE WNA16 method:
+    uint8 [N, K/2], byte (n, j) = nibble(k=2j) | nibble(k=2j+1) << 4
+    (vLLM: model_executor/layers/quantization/moe_wna16.py:389-425, tensor_type "qweight")."""
+    q = unpack_awq(qweight)                       # [K, N] nibbles in column order
+    t = np.ascontiguousarray(q.T)                 # [N, K]
+    return (t[:, 0::2] | (t[:, 1::2] << 4)).astype(np.uint8)
+
+
+def awq_to_wna16_qzeros(qzeros) -> np.ndarray:
+    """AWQ qzeros int32 [K/G, N/8] -> uint8 [N/2, K/G], byte (i, g) = zero(n=2i) |
+    zero(n=2i+1) << 4 (same converter, tensor_type "qzeros")."""
+    z = unpack_awq(qzeros)                        # [K/G, N]
+    t = np.ascontiguousarray(z.T)                 # [N, K/G]
+    return (t[0::2, :] | (t[1::2, :] << 4)).astype(np.uint8)
+
+
+def wna16_to_awq_qweight(w_u8) -> np.ndarray:
+    """Inverse of awq_to_wna16_qweight: uint8 [N, K/2] -> int32 [K, N/8]."""
+    w = np.asarray(w_u8, dtype=np.uint8)
+    n, half = w.shape
+    t = np.empty((n, half * 2), dtype=np.uint8)
+    t[:, 0::2] = w & 0xF
+    t[:, 1::2] = w >> 4
+    return pack_awq(np.ascontiguousarray(t.T))
+
+
+def wna16_to_awq_qzeros(z_u8) -> np.ndarray:
+    """Inverse of awq_to_wna16_qzeros: uint8 [N/2, K/G] -> int32 [K/G, N/8]."""
+    z = np.asarray(z_u8, dtype=np.uint8)
+    half, groups = z.shape
+    t = np.empty((half * 2, groups), dtype=np.uint8)
+    t[0::2, :] = z & 0xF
+    t[1::2, :] = z >> 4
+    return pack_awq(np.ascontiguousarray(t.T))
+
+
 def awq_linear(x, qweight, scales, qzeros, bias=None, group: int = 128) -> np.ndarray:
     """AWQLinearMethod.apply: fp16 output, optional bias added after the product.
 

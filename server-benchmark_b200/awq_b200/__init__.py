@@ -10,7 +10,7 @@ from ._lib import (KERNEL_AUTO, KERNEL_GENERIC, KERNEL_STREAM, KERNEL_STREAM_EXA
                    KERNEL_TCGEN05, KERNEL_TS, KERNEL_TS_EXACT, KERNEL_WT, KERNEL_STREAM_RP, KERNEL_Q8,
                    AwqB200Error)
 from .ops import (awq_dequantize, awq_gemm, awq_repack, awq_repack_kmajor, fused_experts, fused_moe, fused_topk,  # noqa: F401
-                  moe_align_block_size, moe_workspace_bytes, reserve_workspace)
+                  moe_align_block_size, moe_workspace_bytes, reserve_workspace, wna16_to_awq)
 from .linear import AWQConfig, AWQLinearMethod, AWQLinear  # noqa: F401
 
 __version__ = "0.1"

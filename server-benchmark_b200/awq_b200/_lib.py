@@ -40,6 +40,7 @@ PROTOTYPES = {
     "awq_b200_selftest_wait": (c_int, [c_uint, c_void_p]),
     "awq_b200_repack_kmajor_bytes": (c_size_t, [c_int, c_int]),
     "awq_b200_repack_kmajor": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "awq_b200_wna16_to_awq": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_void_p]),
     "awq_b200_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_void_p]),
     "awq_b200_moe_sorted_capacity": (c_int64, [c_int64, c_int, c_int]),

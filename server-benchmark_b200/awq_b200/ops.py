@@ -207,6 +207,33 @@ def awq_repack_kmajor(qweight: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def wna16_to_awq(w: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
+                 group_size: int = 128):
+    """Stacked expert tensors in the byte layout of vLLM's MoE WNA16 method (w uint8 [E, N, K/2],
+    scales fp16 [E, N, K/G], zeros uint8 [E, N/2, K/G]; moe_wna16.py:252-324) -> the AWQ
+    checkpoint layout ``fused_experts`` takes: (qweight i32 [E, K, N/8], scales f16 [E, K/G, N],
+    qzeros i32 [E, K/G, N/8]).  Load time; bit-exact inverse of vLLM's converter
+    (moe_wna16.py:389-425)."""
+    _require(w, "w", torch.uint8, 3)
+    _require(scales, "scales", torch.float16, 3)
+    _require(zeros, "zeros", torch.uint8, 3)
+    e, n, half = w.shape
+    k = 2 * half
+    if n % PACK_FACTOR != 0 or k % group_size != 0:
+        raise ValueError("N must be a multiple of 8 and K a multiple of the group size")
+    g = k // group_size
+    if scales.shape != (e, n, g) or zeros.shape != (e, n // 2, g):
+        raise ValueError("scales / zeros shapes do not match w and the group size")
+    qweight = torch.empty((e, k, n // PACK_FACTOR), dtype=torch.int32, device=w.device)
+    qzeros = torch.empty((e, g, n // PACK_FACTOR), dtype=torch.int32, device=w.device)
+    s_out = torch.empty((e, g, n), dtype=torch.float16, device=w.device)
+    rc = _lib.load().awq_b200_wna16_to_awq(w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                           qweight.data_ptr(), s_out.data_ptr(),
+                                           qzeros.data_ptr(), e, n, k, group_size, _stream())
+    _lib.check("awq_b200_wna16_to_awq", rc)
+    return qweight, s_out, qzeros
+
+
 # ------------------------------------------------------------------------------- MoE
 
 

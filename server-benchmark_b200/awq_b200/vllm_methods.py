@@ -10,6 +10,8 @@ from vllm.model_executor.layers.fused_moe import (FusedMoEMethodBase,
 from vllm.model_executor.layers.linear import LinearBase, UnquantizedLinearMethod
 from vllm.model_executor.layers.quantization.awq import AWQConfig, AWQLinearMethod
 from vllm.model_executor.layers.quantization.awq_marlin import AWQMarlinConfig
+from vllm.model_executor.layers.quantization.moe_wna16 import (MoeWNA16Config, MoeWNA16Method,
+                                                                 is_layer_skipped_quant)
 from vllm.model_executor.layers.quantization.utils.quant_utils import is_layer_skipped
 from vllm.model_executor.utils import set_weight_attrs
 
@@ -164,3 +166,69 @@ class B200AWQMarlinConfig(AWQMarlinConfig):
 
     def get_quant_method(self, layer, prefix):
         return quant_method_for(self, AWQMarlinConfig, layer, prefix)
+
+
+class B200MoeWNA16Method(MoeWNA16Method):
+    """MoeWNA16Method (moe_wna16.py:208-512) with its parameter declaration and checkpoint
+    loader unchanged -- the loader converts AWQ expert tensors to uint8 [E, N, K/2] while it
+    loads -- and, once loading is over, the tensors converted back to the AWQ layout the expert
+    kernels read (one pass at load time, ``ops.wna16_to_awq``)."""
+
+    def process_weights_after_loading(self, layer) -> None:
+        g = layer.group_size
+        if _options["dummy_fill"] is not None:
+            gen = torch.Generator(device=layer.w13_qweight.device).manual_seed(
+                _options["dummy_fill"] + _name_seed(layer))
+            for name in ("w13_qweight", "w2_qweight", "w13_qzeros", "w2_qzeros"):
+                p = getattr(layer, name)
+                p.data.copy_(torch.randint(0, 256, p.shape, dtype=torch.int32, device=p.device,
+                                           generator=gen).to(torch.uint8))
+            for name in ("w13_scales", "w2_scales"):
+                p = getattr(layer, name)
+                p.data.copy_((0.002 + 0.018 * torch.rand(p.shape, device=p.device,
+                                                         generator=gen)).to(p.dtype))
+        for proj in ("w13", "w2"):
+            q, s, z = ops.wna16_to_awq(getattr(layer, proj + "_qweight").data.contiguous(),
+                                       getattr(layer, proj + "_scales").data.contiguous(),
+                                       getattr(layer, proj + "_qzeros").data.contiguous(), g)
+            for name, t in (("_qweight", q), ("_scales", s), ("_qzeros", z)):
+                setattr(layer, proj + name, torch.nn.Parameter(t, requires_grad=False))
+        self.moe_quant_config = None
+
+    def get_fused_moe_quant_config(self, layer):
+        from vllm.model_executor.layers.fused_moe.config import int4_w4a16_moe_quant_config
+        return int4_w4a16_moe_quant_config(
+            w1_scale=layer.w13_scales, w2_scale=layer.w2_scales, w1_zp=layer.w13_qzeros,
+            w2_zp=layer.w2_qzeros, block_shape=[0, layer.group_size])
+
+    def apply(self, layer, x, topk_weights, topk_ids, shared_experts=None,
+              shared_experts_input=None):
+        calls["moe"] += 1
+        if x.dtype != torch.float16:
+            raise ValueError("AWQ on B200 computes in fp16: start vLLM with --dtype half")
+        if self.moe_quant_config is None:
+            self.moe_quant_config = self.get_fused_moe_quant_config(layer)
+        act = getattr(layer, "activation", "silu")
+        return ops.fused_experts(
+            x.contiguous(), layer.w13_qweight, layer.w2_qweight,
+            topk_weights.to(torch.float32).contiguous(), topk_ids.to(torch.int32).contiguous(),
+            activation=str(getattr(act, "value", act)),
+            apply_router_weight_on_input=getattr(layer, "apply_router_weight_on_input", False),
+            global_num_experts=getattr(layer, "global_num_experts", -1),
+            expert_map=getattr(layer, "expert_map", None), quant_config=self.moe_quant_config)
+
+
+class B200MoeWNA16Config(MoeWNA16Config):
+    """``moe_wna16`` (moe_wna16.py:34-206) handing out the B200 methods for AWQ checkpoints;
+    GPTQ checkpoints and shapes the expert kernels do not take stay on vLLM's own methods."""
+
+    def get_quant_method(self, layer, prefix):
+        awq = self.linear_quant_method in ("awq", "awq_marlin") and self.weight_bits == 4 \
+            and self.has_zp
+        if not awq or is_layer_skipped_quant(prefix, self.modules_to_not_convert):
+            return MoeWNA16Config.get_quant_method(self, layer, prefix)
+        if isinstance(layer, LinearBase):
+            return B200AWQConfig.from_config(self.full_config).get_quant_method(layer, prefix)
+        if isinstance(layer, RoutedExperts) and moe_supported(layer, self.group_size):
+            return B200MoeWNA16Method(self, layer.moe_config)
+        return MoeWNA16Config.get_quant_method(self, layer, prefix)

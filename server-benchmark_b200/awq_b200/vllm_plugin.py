@@ -4,7 +4,7 @@ Two hooks, both installed by ``register()`` (entry point of group ``vllm.general
 pyproject.toml next to this package; vLLM loads those in the API server, the engine core and
 every worker, vllm/plugins/__init__.py:28-82; the function is idempotent, as vLLM requires):
 
-1. **Quantization configs.**  ``"awq"`` and ``"awq_marlin"`` are re-registered
+1. **Quantization configs.**  ``"awq"``, ``"awq_marlin"`` and ``"moe_wna16"`` are re-registered
    (vllm/model_executor/layers/quantization/__init__.py:59-106: a registered config replaces the
    built-in of the same name).  vLLM started without ``--quantization`` turns every AWQ
    checkpoint into ``awq_marlin`` (awq_marlin.py:249-278), so that name has to be covered for the
@@ -15,6 +15,9 @@ every worker, vllm/plugins/__init__.py:28-82; the function is idempotent, as vLL
      * ``B200AWQMoEMethod`` for fused-MoE layers: the AWQ-layout stacked parameters of
        awq_marlin.py:549-623 kept as they are, ``apply`` with the signature of
        fused_moe_method_base.py:163-172 calling the expert kernels of this package.
+   Under ``--quantization moe_wna16`` the expert layers keep that method's parameter layout
+   and loader (uint8 [E, N, K/2], moe_wna16.py:252-324,387-512) and are converted back to the
+   AWQ layout once after loading (``B200MoeWNA16Method``).
    Layers the kernels cannot take (group sizes other than 32/64/128 for experts, odd hidden
    sizes) fall back to what stock vLLM would have picked.
 2. **Operator overrides.**  ``torch.ops._C.awq_gemm`` / ``awq_dequantize`` are re-implemented for
@@ -82,8 +85,10 @@ def _build_methods():
     from . import vllm_methods as vm
     register_quantization_config("awq")(vm.B200AWQConfig)
     register_quantization_config("awq_marlin")(vm.B200AWQMarlinConfig)
+    register_quantization_config("moe_wna16")(vm.B200MoeWNA16Config)
     return {"linear": vm.B200AWQLinearMethod, "moe": vm.B200AWQMoEMethod,
-            "awq": vm.B200AWQConfig, "awq_marlin": vm.B200AWQMarlinConfig}
+            "awq": vm.B200AWQConfig, "awq_marlin": vm.B200AWQMarlinConfig,
+            "moe_wna16": vm.B200MoeWNA16Config, "moe_wna16_method": vm.B200MoeWNA16Method}
 
 
 classes: dict = {}

@@ -115,6 +115,22 @@ int awq_b200_repack_kmajor(const void* qweight, void* out, int K, int N, void* s
                                    static_cast<cudaStream_t>(stream));
 }
 
+int awq_b200_wna16_to_awq(const void* w, const void* scales, const void* zeros, void* qweight,
+                          void* scales_out, void* qzeros, int E, int N, int K, int group,
+                          void* stream) {
+  if (!w || !scales || !zeros || !qweight || !scales_out || !qzeros) return AWQ_B200_ERR_NULL;
+  if (E <= 0 || N <= 0 || K <= 0 || group <= 0) return AWQ_B200_ERR_SHAPE;
+  if (N % awq::kPack != 0 || K % 2 != 0 || K % group != 0) return AWQ_B200_ERR_SHAPE;
+  if (int rc = check_device()) return rc;
+  return awq::launch_wna16_to_awq(static_cast<const uint8_t*>(w),
+                                  static_cast<const __half*>(scales),
+                                  static_cast<const uint8_t*>(zeros),
+                                  static_cast<uint32_t*>(qweight),
+                                  static_cast<__half*>(scales_out),
+                                  static_cast<uint32_t*>(qzeros), E, N, K, group,
+                                  static_cast<cudaStream_t>(stream));
+}
+
 size_t awq_b200_gemm_workspace_bytes(int M, int N, int K, int group, int kernel) {
   if (M <= 0 || check_awq_shape(N, K, group) != AWQ_B200_OK) return 0;
   if (kernel == AWQ_B200_KERNEL_Q8) return awq::gemm_q8_workspace_bytes(M, N, K, group);

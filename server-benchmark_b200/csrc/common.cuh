@@ -196,6 +196,10 @@ int launch_gemm_q8(const __half* x, const void* qweight_km, const __half* scales
 void q8_set_spin_limit(uint32_t polls);
 int launch_wait_selftest(uint32_t polls, cudaStream_t stream);
 int q8_device_status(int* out, int clear);
+// wna16.cu: expert weights from the MoE WNA16 byte layout back to the AWQ checkpoint layout
+int launch_wna16_to_awq(const uint8_t* w, const __half* scales, const uint8_t* zeros,
+                        uint32_t* qweight, __half* scales_out, uint32_t* qzeros, int E, int N,
+                        int K, int group, cudaStream_t stream);
 bool moe_wt_supported(int H, int I, int group);
 int launch_wt_grouped(int mode, const __half* a, int64_t a_rows, const uint32_t* w, int experts,
                       const __half* scales, const uint32_t* qzeros, const float* topk_weights,

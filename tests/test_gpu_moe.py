@@ -135,6 +135,32 @@ def test_fused_experts_vs_oracle(A, e, h, i, t, k):
     assert O.rel_err(y2, ref) < TOL
 
 
+def test_wna16_layout_converts_back_bit_exact(A, golden):
+    """uint8 [E, N, K/2] (vLLM's MoE WNA16 layout) -> AWQ layout on the device: vLLM's own
+    converted tensors give back the AWQ tensors they were made from, and stacked random experts
+    agree with the oracle's conversion."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden",
+                             "wna16_golden.npz"))
+    for name in ("small", "wide", "g64"):
+        grp = int(g[f"{name}.group"][0])
+        q, s, z = A.wna16_to_awq(torch.from_numpy(g[f"{name}.wna16_qweight"])[None].cuda(),
+                                 torch.from_numpy(g[f"{name}.wna16_scales"])[None].cuda(),
+                                 torch.from_numpy(g[f"{name}.wna16_qzeros"])[None].cuda(), grp)
+        assert np.array_equal(q[0].cpu().numpy(), g[f"{name}.qweight"])
+        assert np.array_equal(z[0].cpu().numpy(), g[f"{name}.qzeros"])
+        assert np.array_equal(s[0].cpu().numpy(), g[f"{name}.scales"])
+    w1, w2, _, _ = _moe_case(6, 384, 160, 1, 2, seed=3)     # ragged tiles: N = 320 / 384, K = 384 / 160
+    for qw, sc, qz in (w1, w2):
+        wu = np.stack([O.awq_to_wna16_qweight(a) for a in qw.numpy()])
+        zu = np.stack([O.awq_to_wna16_qzeros(a) for a in qz.numpy()])
+        su = np.ascontiguousarray(sc.numpy().transpose(0, 2, 1))
+        grp = qw.shape[1] // sc.shape[1]
+        q, s, z = A.wna16_to_awq(torch.from_numpy(wu).cuda(), torch.from_numpy(su).cuda(),
+                                 torch.from_numpy(zu).cuda(), grp)
+        assert torch.equal(q.cpu(), qw) and torch.equal(z.cpu(), qz) and torch.equal(s.cpu(), sc)
+
+
 def test_fused_experts_accepts_the_reference_call_form(A):
     """w1 / w2 as the stacked qweight tensors plus a quant_config object carrying scales and zero
     points (vLLM fused_moe.py:1587-1599) gives the same bits as the triple form."""

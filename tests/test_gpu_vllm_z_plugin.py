@@ -57,8 +57,11 @@ def _resolve_quant_config(user_quant=None):
     from vllm.model_executor.layers.quantization import get_quantization_config
     name = get_quantization_config("awq_marlin").override_quantization_method(HF_QUANT,
                                                                                user_quant)
+    if name is None and user_quant is not None:
+        name = get_quantization_config(user_quant).override_quantization_method(
+            HF_QUANT, user_quant) or user_quant
     if name is None:
-        name = user_quant or HF_QUANT["quant_method"]
+        name = HF_QUANT["quant_method"]
     return name, get_quantization_config(name).from_config(HF_QUANT)
 
 
@@ -173,6 +176,45 @@ def test_vllm_fused_moe_layer_runs_our_kernels(env, t):
         y = moe(x.cuda(), logits.cuda())
     assert vllm_plugin.calls["moe"] == before + 1
     assert y.shape == (t, h) and y.dtype == torch.float16
+    wts, ids, _ = O.topk_softmax(logits.numpy(), topk, True)
+    ref = O.fused_experts_fp32(x.numpy(), *[a.numpy() for a in w1], *[a.numpy() for a in w2],
+                               wts, ids, 128)
+    assert O.rel_err(y.float().cpu().numpy(), ref) < TOL
+    assert _status() == 0
+
+
+def test_moe_wna16_route_runs_our_kernels(env):
+    """--quantization moe_wna16 on an AWQ checkpoint: vLLM's MoeWNA16 parameters and loader, the
+    plug-in's method; the layer is loaded with tensors in that method's byte layout."""
+    from vllm.forward_context import set_forward_context
+    from vllm.model_executor.layers.fused_moe import FusedMoE
+    from awq_b200 import synth, vllm_plugin
+    name, qc = _resolve_quant_config("moe_wna16")
+    assert name == "moe_wna16" and type(qc) is vllm_plugin.classes["moe_wna16"]
+    e, topk, h, inter, t = 16, 4, 512, 256, 24
+    moe = FusedMoE(num_experts=e, top_k=topk, hidden_size=h, intermediate_size=inter,
+                   params_dtype=torch.float16, renormalize=True, quant_config=qc,
+                   prefix="model.layers.77.mlp.experts")
+    assert type(moe.quant_method) is vllm_plugin.classes["moe_wna16_method"]
+    assert moe.w13_qweight.dtype == torch.uint8
+    assert tuple(moe.w13_qweight.shape) == (e, 2 * inter, h // 2)
+    w1, w2 = synth.moe_layer_tensors(e, h, inter, 128, seed=21)
+    moe.cuda()
+    for proj, (qw, sc, qz) in (("w13", w1), ("w2", w2)):
+        getattr(moe, proj + "_qweight").data.copy_(torch.from_numpy(
+            np.stack([O.awq_to_wna16_qweight(a) for a in qw.numpy()])))
+        getattr(moe, proj + "_qzeros").data.copy_(torch.from_numpy(
+            np.stack([O.awq_to_wna16_qzeros(a) for a in qz.numpy()])))
+        getattr(moe, proj + "_scales").data.copy_(sc.transpose(1, 2))
+    moe.quant_method.process_weights_after_loading(moe)
+    assert moe.w13_qweight.dtype == torch.int32 and torch.equal(moe.w13_qweight.cpu(), w1[0])
+    assert torch.equal(moe.w2_qzeros.cpu(), w2[2])
+    x = synth.activations(t, h, seed=t)
+    logits = torch.randn(t, e, generator=torch.Generator().manual_seed(t))
+    before = vllm_plugin.calls["moe"]
+    with torch.inference_mode(), set_forward_context(None, env, num_tokens=t):
+        y = moe(x.cuda(), logits.cuda())
+    assert vllm_plugin.calls["moe"] == before + 1
     wts, ids, _ = O.topk_softmax(logits.numpy(), topk, True)
     ref = O.fused_experts_fp32(x.numpy(), *[a.numpy() for a in w1], *[a.numpy() for a in w2],
                                wts, ids, 128)

@@ -145,3 +145,19 @@ def test_pack_kmajor_layout():
         assert km[slab, g, r, b] == (lo | (hi << 4))
     assert not km[1, :, 8:, :].any()    # padding columns
     assert km.size == 2 * 2 * 256 * 64
+
+
+def test_wna16_layout_against_vllm_converter():
+    """The MoE WNA16 byte layout as vLLM's own weight-loader converter produces it
+    (tests/golden/make_wna16_golden.py), both directions, bit-exact."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden",
+                             "wna16_golden.npz"))
+    for name in ("small", "wide", "g64"):
+        w = O.awq_to_wna16_qweight(g[f"{name}.qweight"])
+        z = O.awq_to_wna16_qzeros(g[f"{name}.qzeros"])
+        assert np.array_equal(w, g[f"{name}.wna16_qweight"])
+        assert np.array_equal(z, g[f"{name}.wna16_qzeros"])
+        assert np.array_equal(g[f"{name}.wna16_scales"], g[f"{name}.scales"].T)
+        assert np.array_equal(O.wna16_to_awq_qweight(w), g[f"{name}.qweight"])
+        assert np.array_equal(O.wna16_to_awq_qzeros(z), g[f"{name}.qzeros"])
