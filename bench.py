@@ -654,6 +654,14 @@ def run_moe(dev, stream):
     return out
 
 
+def _device_status() -> int:
+    import ctypes
+    from awq_b200 import _lib
+    v = ctypes.c_int(-1)
+    _lib.load().awq_b200_device_status_clear(ctypes.byref(v))
+    return v.value
+
+
 def run_tp(args, world, rank, dev, stream, barrier):
     """The same layer sharded over `world` GPUs: qkv/gate_up column-parallel, o_proj/down
     row-parallel with the fp16 [M, 8192] partial outputs all-reduced over NVLink (NCCL).  The
@@ -690,6 +698,27 @@ def run_tp(args, world, rank, dev, stream, barrier):
                         else tp.row_parallel_forward(x, sh))
         return outs
 
+    # the same step with the one-shot peer-memory all-reduce fed directly by the GEMM epilogue
+    comm, comm_note = None, None
+    try:
+        comm = tp.PeerAllReduce(m * 8192 * 2)
+    except Exception as e:
+        comm_note = f"{type(e).__name__}: {str(e)[:160]}"
+    ok = torch.tensor([0 if comm is None else 1], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok[0]) == 0:
+        comm = None
+
+    def step_peer():
+        outs, call = [], 0
+        for (kind, sh), x in zip(shards, xs):
+            if kind == "col":
+                outs.append(tp.column_parallel_forward(x, sh))
+            else:
+                outs.append(tp.row_parallel_forward(x, sh, comm=comm, slot=tp.slot_for_call(call)))
+                call += 1
+        return outs
+
     # ---- parity: the all-reduced row-parallel outputs against the unsharded product ----
     outs = step()
     torch.cuda.synchronize()
@@ -700,9 +729,18 @@ def run_tp(args, world, rank, dev, stream, barrier):
         ref = awq_b200.awq_gemm(f[0], f[1], f[2], f[3], 8).float()
         err = float((o.float() - ref).abs().max() / ref.abs().max())
         worst = max(worst, err)
-    t = torch.tensor([worst], device=dev, dtype=torch.float64)
+    worst_peer = 0.0
+    if comm is not None:
+        outs_peer = step_peer()
+        torch.cuda.synchronize()
+        for o, f in zip(outs_peer, full):
+            if f is None:
+                continue
+            ref = awq_b200.awq_gemm(f[0], f[1], f[2], f[3], 8).float()
+            worst_peer = max(worst_peer, float((o.float() - ref).abs().max() / ref.abs().max()))
+    t = torch.tensor([worst, worst_peer], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    parity = float(t[0])
+    parity, parity_peer = float(t[0]), float(t[1])
     del full
 
     def timed(fn, steps):
@@ -746,8 +784,25 @@ def run_tp(args, world, rank, dev, stream, barrier):
         sec_no_ar = timed(g2.replay, steps)
     except Exception:
         pass
-    sec = sec_graph if sec_graph is not None else sec_eager
+    sec_peer = sec_peer_eager = None
+    if comm is not None:
+        sec_peer_eager = timed(step_peer, steps)
+        g3 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g3, stream=stream):
+            step_peer()
+        sec_peer = timed(g3.replay, steps)
+        outs_replay = step_peer()      # the replays left the call numbering consistent
+        torch.cuda.synchronize()
+    sec = min(x for x in (sec_graph, sec_eager, sec_peer) if x is not None)
     res = {"parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": sec * 1e3,
+           "ms_per_step_graph_peer_all_reduce": None if sec_peer is None else sec_peer * 1e3,
+           "ms_per_step_eager_peer_all_reduce":
+               None if sec_peer_eager is None else sec_peer_eager * 1e3,
+           "parity_rel_err_peer_all_reduce": parity_peer if comm is not None else None,
+           "peer_all_reduce": "one-shot kernel over peer-mapped regions, GEMM writes its partial "
+                              "into the region (awq_b200_allreduce)" if comm is not None
+                              else f"unavailable: {comm_note}",
+           "device_status": _device_status(),
            "ms_per_step_eager": sec_eager * 1e3,
            "ms_per_step_graph": None if sec_graph is None else sec_graph * 1e3,
            "ms_per_step_graph_without_all_reduce": None if sec_no_ar is None else sec_no_ar * 1e3,

@@ -160,10 +160,46 @@ int awq_b200_device_status_clear(int* status);
 
 /*
  * Number of polls after which a CTA of the AWQ_B200_KERNEL_Q8 kernel stops waiting for another
- * CTA's partial tile (0 restores the default, 2^20).  Process-wide; meant for tests that check the
+ * CTA's partial tile (0 restores the default, 2^20), and after which awq_b200_allreduce stops
+ * waiting for a peer (default 2^22).  Process-wide; meant for tests that check the
  * give-up path with a tiny limit.  No counterpart in the reference.
  */
 void awq_b200_set_wait_limit(unsigned int polls);
+
+/*
+ * One-shot all-reduce (sum) of fp16 partial outputs over peer memory, for the row-parallel linears
+ * of a tensor-parallel model: replaces the all-reduce behind RowParallelLinear.forward
+ * (vllm/model_executor/layers/linear.py:1556-1559; vLLM's own small-message path is
+ * distributed/device_communicators/custom_all_reduce.py:232-245).
+ *
+ * Every rank owns one region of device memory that all `world` ranks (one process per GPU, one
+ * node) have mapped; regions[r] is rank r's region as mapped in THIS process (regions[rank] is
+ * the local one).  A region starts with AWQ_B200_AR_FLAG_BYTES of flags, zero when the first call
+ * is made; the partial of this call lies at `data_offset` (>= AWQ_B200_AR_FLAG_BYTES, a multiple
+ * of 16, the same on all ranks) and is `bytes` long (a multiple of 16).  All ranks make the same
+ * sequence of calls.  The kernel tells its peers that the partial is complete, waits for theirs,
+ * adds the `world` partials in rank order in fp32 and writes fp16 to `out` (local memory).
+ * `state`: 8 bytes of local device memory, zero before the first call, private to this sequence
+ * of calls (it numbers the calls on the device, so a CUDA graph that holds the call can be
+ * replayed).  flags: bit 0 = also wait, before returning, until every peer has finished reading
+ * (needed when the next call uses the same data_offset; a caller that alternates between two
+ * offsets does not need it: a rank cannot start call i+2 before every peer has left call i);
+ * bit 1 = programmatic dependent launch after the kernel that writes the partial.
+ * Peer memory is read with plain loads; nothing is bound to a multicast object.  Waits are
+ * bounded (awq_b200_set_wait_limit); one that runs out leaves 70 + peer (start) or 80 + peer
+ * (end) in the status word, `out` incomplete, and the call numbering of the ranks out of step.
+ */
+#define AWQ_B200_AR_MAX_RANKS 8
+#define AWQ_B200_AR_MAX_BLOCKS 32
+#define AWQ_B200_AR_FLAG_BYTES 4096
+int awq_b200_allreduce(const void* const* regions, int rank, int world, size_t data_offset,
+                       void* out, size_t bytes, void* state, int flags, void* stream);
+
+/*
+ * cudaDeviceEnablePeerAccess from the current device to `peer_device` (already enabled counts as
+ * success).  Needed once per peer before awq_b200_allreduce dereferences that peer's region.
+ */
+int awq_b200_enable_peer_access(int peer_device);
 
 /*
  * Runs the give-up path of the bounded waits once: a one-warp kernel waits, with a limit of

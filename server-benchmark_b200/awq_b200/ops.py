@@ -121,11 +121,12 @@ def awq_dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Ten
 
 def awq_gemm(input: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
              qzeros: torch.Tensor, split_k_iters: int = 8, *, bias: torch.Tensor | None = None,
-             kernel: int = _lib.KERNEL_AUTO) -> torch.Tensor:
+             kernel: int = _lib.KERNEL_AUTO, out: torch.Tensor | None = None) -> torch.Tensor:
     """y fp16 [M, N] = input [M, K] @ dequant(qweight), fp32 accumulation.
 
     ``split_k_iters`` is accepted and ignored (the split along K is chosen from the shape and
-    the SM count).  ``bias`` and ``kernel`` are keyword-only extensions.
+    the SM count).  ``bias``, ``kernel`` and ``out`` (a contiguous fp16 [M, N] tensor to write
+    into, e.g. a view of a peer-mapped buffer) are keyword-only extensions.
     """
     k, n, group = _awq_dims(qweight, scales, qzeros, kmajor=kernel == _lib.KERNEL_Q8)
     _require(input, "input", torch.float16, 2)
@@ -136,7 +137,12 @@ def awq_gemm(input: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
         if bias.shape[0] != n:
             raise ValueError(f"bias must have {n} elements")
     m = input.shape[0]
-    out = torch.empty((m, n), dtype=torch.float16, device=input.device)
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float16, device=input.device)
+    else:
+        _require(out, "out", torch.float16, 2)
+        if out.shape != (m, n):
+            raise ValueError(f"out must be [{m}, {n}]")
     if m == 0:
         return out
     lib = _lib.load()

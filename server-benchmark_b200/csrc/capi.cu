@@ -207,13 +207,14 @@ int awq_b200_gemm(const void* x, const void* qweight, const void* scales, const 
 static int device_status(int* status, int clear) {
   if (!status) return AWQ_B200_ERR_NULL;
   if (int rc = check_device()) return rc;
-  int v[4] = {0, 0, 0, 0};
+  int v[5] = {0, 0, 0, 0, 0};
   if (int rc = awq::tc_device_status(&v[0], clear)) return rc;
   if (int rc = awq::ts_device_status(&v[1], clear)) return rc;
   if (int rc = awq::wt_device_status(&v[2], clear)) return rc;
   if (int rc = awq::q8_device_status(&v[3], clear)) return rc;
+  if (int rc = awq::ar_device_status(&v[4], clear)) return rc;
   *status = 0;
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 5; ++i)
     if (v[i] != 0 && *status == 0) *status = v[i];
   return AWQ_B200_OK;
 }
@@ -222,7 +223,43 @@ int awq_b200_device_status(int* status) { return device_status(status, 0); }
 
 int awq_b200_device_status_clear(int* status) { return device_status(status, 1); }
 
-void awq_b200_set_wait_limit(unsigned int polls) { awq::q8_set_spin_limit(polls); }
+void awq_b200_set_wait_limit(unsigned int polls) {
+  awq::q8_set_spin_limit(polls);
+  awq::ar_set_spin_limit(polls);
+}
+
+int awq_b200_enable_peer_access(int peer_device) {
+  if (int rc = check_device()) return rc;
+  int dev = -1, can = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
+  if (peer_device == dev) return AWQ_B200_OK;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can)
+    return AWQ_B200_ERR_DEVICE;
+  const cudaError_t err = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (err == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return AWQ_B200_OK;
+  }
+  return err == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
+int awq_b200_allreduce(const void* const* regions, int rank, int world, size_t data_offset,
+                       void* out, size_t bytes, void* state, int flags, void* stream) {
+  if (!regions || !out || !state) return AWQ_B200_ERR_NULL;
+  if (world < 1 || world > AWQ_B200_AR_MAX_RANKS || rank < 0 || rank >= world)
+    return AWQ_B200_ERR_SHAPE;
+  if (bytes == 0) return AWQ_B200_OK;
+  if (bytes % 16 != 0 || data_offset % 16 != 0 || data_offset < AWQ_B200_AR_FLAG_BYTES)
+    return AWQ_B200_ERR_SHAPE;
+  for (int r = 0; r < world; ++r) {
+    if (!regions[r]) return AWQ_B200_ERR_NULL;
+    if (!aligned16(regions[r])) return AWQ_B200_ERR_ALIGN;
+  }
+  if (!aligned16(out)) return AWQ_B200_ERR_ALIGN;
+  if (int rc = check_device()) return rc;
+  return awq::launch_allreduce(regions, data_offset, out, bytes, state, rank, world, flags,
+                               static_cast<cudaStream_t>(stream));
+}
 
 int awq_b200_selftest_wait(unsigned int polls, void* stream) {
   if (int rc = check_device()) return rc;

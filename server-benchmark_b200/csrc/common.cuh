@@ -196,6 +196,12 @@ int launch_gemm_q8(const __half* x, const void* qweight_km, const __half* scales
 void q8_set_spin_limit(uint32_t polls);
 int launch_wait_selftest(uint32_t polls, cudaStream_t stream);
 int q8_device_status(int* out, int clear);
+// allreduce.cu: one-shot all-reduce of fp16 partial outputs over peer memory
+int launch_allreduce(const void* const* regions, size_t data_offset, void* out, size_t bytes,
+                     void* state, int rank, int world, int flags, cudaStream_t stream);
+void ar_set_spin_limit(uint32_t polls);
+int ar_device_status(int* out, int clear);
+
 // wna16.cu: expert weights from the MoE WNA16 byte layout back to the AWQ checkpoint layout
 int launch_wna16_to_awq(const uint8_t* w, const __half* scales, const uint8_t* zeros,
                         uint32_t* qweight, __half* scales_out, uint32_t* qzeros, int E, int N,
