@@ -704,10 +704,6 @@ def run_tp(args, world, rank, dev, stream, barrier):
         comm = tp.PeerAllReduce(m * 8192 * 2)
     except Exception as e:
         comm_note = f"{type(e).__name__}: {str(e)[:160]}"
-    ok = torch.tensor([0 if comm is None else 1], device=dev)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if int(ok[0]) == 0:
-        comm = None
 
     def step_peer():
         outs, call = [], 0
@@ -791,7 +787,7 @@ def run_tp(args, world, rank, dev, stream, barrier):
         with torch.cuda.graph(g3, stream=stream):
             step_peer()
         sec_peer = timed(g3.replay, steps)
-        outs_replay = step_peer()      # the replays left the call numbering consistent
+        step_peer()                    # the replays left the call numbering consistent
         torch.cuda.synchronize()
     sec = min(x for x in (sec_graph, sec_eager, sec_peer) if x is not None)
     res = {"parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": sec * 1e3,
@@ -811,6 +807,9 @@ def run_tp(args, world, rank, dev, stream, barrier):
            "collective": "nccl all_reduce fp16 [16, 8192] after o_proj and down"}
     if sec_graph is None:
         res["graph_note"] = graph_note
+    if comm is not None:
+        del g3
+        comm.close()
     return res
 
 

@@ -184,7 +184,8 @@ void awq_b200_set_wait_limit(unsigned int polls);
  * replayed).  flags: bit 0 = also wait, before returning, until every peer has finished reading
  * (needed when the next call uses the same data_offset; a caller that alternates between two
  * offsets does not need it: a rank cannot start call i+2 before every peer has left call i);
- * bit 1 = programmatic dependent launch after the kernel that writes the partial.
+ * bit 1 = programmatic dependent launch after the kernel that writes the partial (measured 1.4 us
+ * slower per call than a plain launch behind the decode GEMMs: off in the Python host).
  * Peer memory is read with plain loads; nothing is bound to a multicast object.  Waits are
  * bounded (awq_b200_set_wait_limit); one that runs out leaves 70 + peer (start) or 80 + peer
  * (end) in the status word, `out` incomplete, and the call numbering of the ranks out of step.
@@ -196,10 +197,21 @@ int awq_b200_allreduce(const void* const* regions, int rank, int world, size_t d
                        void* out, size_t bytes, void* state, int flags, void* stream);
 
 /*
- * cudaDeviceEnablePeerAccess from the current device to `peer_device` (already enabled counts as
- * success).  Needed once per peer before awq_b200_allreduce dereferences that peer's region.
+ * Set-up of the regions awq_b200_allreduce works on, for one process per GPU on one node.
+ * create: cudaMalloc of `bytes` (>= AWQ_B200_AR_FLAG_BYTES) on the current device, zeroed, and its
+ *         CUDA IPC handle (AWQ_B200_IPC_HANDLE_BYTES bytes) for the other ranks.
+ * open:   maps another rank's region from its handle into the CURRENT device's context
+ *         (cudaIpcOpenMemHandle with lazy peer access: this process's kernels may then dereference
+ *         it).  A handle cannot be opened by the process that created it.
+ * close / destroy undo open / create.  The host moves the handles between processes itself (the
+ * Python host uses torch.distributed.all_gather_object).  vLLM's counterpart:
+ * distributed/device_communicators/custom_all_reduce.py:150-230 (buffer creation and handle exchange).
  */
-int awq_b200_enable_peer_access(int peer_device);
+#define AWQ_B200_IPC_HANDLE_BYTES 64
+int awq_b200_peer_region_create(size_t bytes, void** region, void* handle);
+int awq_b200_peer_region_open(const void* handle, void** region);
+int awq_b200_peer_region_close(void* region);
+int awq_b200_peer_region_destroy(void* region);
 
 /*
  * Runs the give-up path of the bounded waits once: a one-warp kernel waits, with a limit of

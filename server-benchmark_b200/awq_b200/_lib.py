@@ -42,7 +42,10 @@ PROTOTYPES = {
     "awq_b200_repack_kmajor": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "awq_b200_allreduce": (c_int, [c_void_p, c_int, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
                                    c_int, c_void_p]),
-    "awq_b200_enable_peer_access": (c_int, [c_int]),
+    "awq_b200_peer_region_create": (c_int, [c_size_t, c_void_p, c_void_p]),
+    "awq_b200_peer_region_open": (c_int, [c_void_p, c_void_p]),
+    "awq_b200_peer_region_close": (c_int, [c_void_p]),
+    "awq_b200_peer_region_destroy": (c_int, [c_void_p]),
     "awq_b200_wna16_to_awq": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_void_p]),
     "awq_b200_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_void_p]),

@@ -127,11 +127,20 @@ def slot_for_call(call_index: int) -> int:
     return call_index & 1
 
 
+class _DeviceBytes:
+    """Raw device memory as an object torch can alias (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 2}
+
+
 class PeerAllReduce:
     """Peer-mapped regions of the ranks of one node and the one-shot all-reduce over them
-    (``awq_b200_allreduce``).  Set-up is collective over ``group``: every rank allocates its
-    region, the CUDA IPC handles travel through torch.distributed, every rank maps the others'
-    regions and enables peer access.  No multicast object is involved."""
+    (``awq_b200_allreduce``).  Set-up is collective over ``group``: every rank creates its region
+    (``awq_b200_peer_region_create``), the CUDA IPC handles travel through torch.distributed, every
+    rank maps the others' regions into its own device's context (``awq_b200_peer_region_open``).
+    No multicast object is involved."""
 
     def __init__(self, max_bytes: int, group=None, device: torch.device | None = None) -> None:
         self.group = group
@@ -142,30 +151,61 @@ class PeerAllReduce:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.off0, self.off1, size = region_layout(max_bytes)
         self.max_bytes = max_bytes
-        # a dedicated allocation (not a slice of the caching allocator's pool would be shared as a
-        # whole block; the offset inside the block travels with the handle)
-        self.region = torch.zeros(size, dtype=torch.uint8, device=self.device)
-        torch.cuda.synchronize(self.device)
-        info = self.region.untyped_storage()._share_cuda_()
-        infos = [None] * self.world
-        dist.all_gather_object(infos, info, group=group)
         lib = _lib.load()
-        self._peers = []        # keeps the mapped storages alive
-        ptrs = []
-        for r in range(self.world):
-            if r == self.rank:
-                ptrs.append(self.region.data_ptr())
-                continue
-            _lib.check("awq_b200_enable_peer_access",
-                       lib.awq_b200_enable_peer_access(int(infos[r][0])))
-            storage = torch.UntypedStorage._new_shared_cuda(*infos[r])
-            self._peers.append(storage)
-            ptrs.append(storage.data_ptr())
+        self._lib = lib
+        self._opened: list[int] = []
+        self._base = None
+        with torch.cuda.device(self.device):
+            base = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)      # AWQ_B200_IPC_HANDLE_BYTES
+            _lib.check("awq_b200_peer_region_create",
+                       lib.awq_b200_peer_region_create(size, ctypes.byref(base), handle))
+            self._base = base.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            ptrs, failure = [], None
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(self._base)
+                    continue
+                peer = ctypes.c_void_p()
+                rc = lib.awq_b200_peer_region_open(handles[r], ctypes.byref(peer))
+                if rc != 0:
+                    failure = f"rank {self.rank} could not map the region of rank {r} (code {rc})"
+                    break
+                self._opened.append(peer.value)
+                ptrs.append(peer.value)
+            # all ranks leave the constructor the same way
+            ok = torch.tensor([0 if failure else 1], device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok[0]) == 0:
+                for p in self._opened:
+                    lib.awq_b200_peer_region_close(ctypes.c_void_p(p))
+                dist.barrier(group=group)
+                lib.awq_b200_peer_region_destroy(ctypes.c_void_p(self._base))
+                self._base = None
+                raise RuntimeError(failure or "a peer could not map the regions")
         self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        # this rank's region as a tensor, so that the GEMM can be given a view of it as `out`
+        self.region = torch.as_tensor(_DeviceBytes(self._base, size), device=self.device)
         self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
         self.calls = 0
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)   # every region is zeroed and mapped before the first call
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' regions, then frees this rank's."""
+        if self._base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p in self._opened:
+            self._lib.awq_b200_peer_region_close(ctypes.c_void_p(p))
+        self._opened = []
+        dist.barrier(group=self.group)
+        self.region = None
+        self._lib.awq_b200_peer_region_destroy(ctypes.c_void_p(self._base))
+        self._base = None
 
     def fits(self, m: int, n: int) -> bool:
         return 0 < m * n * 2 <= self.max_bytes and (m * n * 2) % 16 == 0
@@ -176,7 +216,7 @@ class PeerAllReduce:
         return self.region[off:off + m * n * 2].view(torch.float16).view(m, n)
 
     def reduce(self, slot: int, m: int, n: int, out: torch.Tensor | None = None,
-               end_barrier: bool = False, dependent_launch: bool = True) -> torch.Tensor:
+               end_barrier: bool = False, dependent_launch: bool = False) -> torch.Tensor:
         if out is None:
             out = torch.empty((m, n), dtype=torch.float16, device=self.device)
         flags = int(end_barrier) | (2 if dependent_launch else 0)
@@ -193,4 +233,4 @@ class PeerAllReduce:
         m, n = partial.shape
         slot = slot_for_call(self.calls)
         self.partial(slot, m, n).copy_(partial)
-        return self.reduce(slot, m, n, dependent_launch=False)
+        return self.reduce(slot, m, n)

@@ -8,7 +8,7 @@
 // custom_all_reduce.py:232-245).  No multicast objects, no TMA: ld/st only.
 //
 // Synchronisation: per block and per peer one 32-bit flag in the peer's region, written with
-// st.release.sys and polled with ld.acquire.sys.  Flags carry the call number (kept in local
+// st.release.sys and polled with relaxed system-scope loads followed by one acquire fence.  Flags carry the call number (kept in local
 // device memory and advanced by the last block of every call, so CUDA-graph replays need no host
 // value), compared with >=, so a peer that is already one call ahead does not confuse a slow
 // block.  Every poll loop has an iteration limit; when it runs out the kernel records a status
@@ -37,10 +37,13 @@ struct ArParams {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
   uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void fence_acquire_sys() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 
 // flag index of (phase, block, writer rank) inside one rank's flag area
@@ -54,12 +57,15 @@ __device__ __forceinline__ bool peer_barrier(const ArParams& p, int phase, uint3
                                              int* s_abort) {
   const int t = threadIdx.x, b = blockIdx.x;
   if (t < p.world && t != p.rank) {
-    __threadfence_system();
+    // release at system scope: everything this thread has observed (the partial written by the
+    // kernel before this one, the loads of this block before the barrier above) is ordered first
     st_release_sys(p.flags[t] + flag_index(phase, b, p.rank), epoch);
     const uint32_t* mine = p.flags[p.rank] + flag_index(phase, b, t);
     bool ok = false;
     for (uint32_t i = 0; i < p.spin_limit; ++i) {
-      if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) {
+      // relaxed polls, one acquire fence once the flag is there
+      if ((int32_t)(ld_relaxed_sys(mine) - epoch) >= 0) {
+        fence_acquire_sys();
         ok = true;
         break;
       }

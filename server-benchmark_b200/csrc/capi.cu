@@ -1,5 +1,6 @@
 // extern "C" boundary of libawq_b200.so: argument validation and kernel selection.
 // Declarations and their reference counterparts: include/awq_b200.h.
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -228,19 +229,51 @@ void awq_b200_set_wait_limit(unsigned int polls) {
   awq::ar_set_spin_limit(polls);
 }
 
-int awq_b200_enable_peer_access(int peer_device) {
+int awq_b200_peer_region_create(size_t bytes, void** region, void* handle) {
+  if (!region || !handle) return AWQ_B200_ERR_NULL;
+  if (bytes < AWQ_B200_AR_FLAG_BYTES) return AWQ_B200_ERR_SHAPE;
   if (int rc = check_device()) return rc;
-  int dev = -1, can = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return AWQ_B200_ERR_LAUNCH;
-  if (peer_device == dev) return AWQ_B200_OK;
-  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can)
-    return AWQ_B200_ERR_DEVICE;
-  const cudaError_t err = cudaDeviceEnablePeerAccess(peer_device, 0);
-  if (err == cudaErrorPeerAccessAlreadyEnabled) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == AWQ_B200_IPC_HANDLE_BYTES, "handle size");
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) {
     (void)cudaGetLastError();
-    return AWQ_B200_OK;
+    return AWQ_B200_ERR_WORKSPACE;
   }
-  return err == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+  cudaIpcMemHandle_t h;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+      cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    cudaFree(p);
+    return AWQ_B200_ERR_LAUNCH;
+  }
+  memcpy(handle, &h, sizeof(h));
+  *region = p;
+  return AWQ_B200_OK;
+}
+
+int awq_b200_peer_region_open(const void* handle, void** region) {
+  if (!handle || !region) return AWQ_B200_ERR_NULL;
+  if (int rc = check_device()) return rc;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  // mapped into the CURRENT device's context, peer access to the owning device enabled with it
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return AWQ_B200_ERR_DEVICE;
+  }
+  *region = p;
+  return AWQ_B200_OK;
+}
+
+int awq_b200_peer_region_close(void* region) {
+  if (!region) return AWQ_B200_ERR_NULL;
+  return cudaIpcCloseMemHandle(region) == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
+}
+
+int awq_b200_peer_region_destroy(void* region) {
+  if (!region) return AWQ_B200_ERR_NULL;
+  return cudaFree(region) == cudaSuccess ? AWQ_B200_OK : AWQ_B200_ERR_LAUNCH;
 }
 
 int awq_b200_allreduce(const void* const* regions, int rank, int world, size_t data_offset,
@@ -257,6 +290,16 @@ int awq_b200_allreduce(const void* const* regions, int rank, int world, size_t d
   }
   if (!aligned16(out)) return AWQ_B200_ERR_ALIGN;
   if (int rc = check_device()) return rc;
+  // every region must be device memory this process has mapped (a stale or foreign pointer is
+  // refused here instead of faulting in the kernel)
+  for (int r = 0; r < world; ++r) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, regions[r]) != cudaSuccess ||
+        attr.type != cudaMemoryTypeDevice) {
+      (void)cudaGetLastError();
+      return AWQ_B200_ERR_DEVICE;
+    }
+  }
   return awq::launch_allreduce(regions, data_offset, out, bytes, state, rank, world, flags,
                                static_cast<cudaStream_t>(stream));
 }

@@ -119,6 +119,8 @@ TWO_RANKS = textwrap.dedent("""
     t = torch.tensor([worst, float(v.value)], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         print("RESULT", float(t[0]), int(t[1]))
+    del g
+    comm.close()
     dist.barrier(); dist.destroy_process_group()
 """)
 
