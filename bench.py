@@ -238,6 +238,34 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------
 
 
+def bind_to_gpu_numa_node(device_index: int) -> dict:
+    """Run this process on the CPUs of the NUMA node its GPU hangs off, so that the pinned host
+    buffers allocated afterwards (first touch) and the copy submissions are local to the GPU's
+    PCIe root.  Reads sysfs only; returns what it did for the JSON line."""
+    import torch
+    try:
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        dev = torch.cuda.get_device_properties(device_index).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        with open(path) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"numa_node": node, "bound": False}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return {"numa_node": node, "bound": False}
+        os.sched_setaffinity(0, allowed)
+        return {"numa_node": node, "bound": True, "cpus": len(allowed)}
+    except Exception as e:   # sysfs not readable in this container: leave the affinity alone
+        return {"bound": False, "note": f"{type(e).__name__}"}
+
+
 def run_cuda(args):
     import torch
     import torch.distributed as dist
@@ -249,6 +277,7 @@ def run_cuda(args):
     if rank == 0:
         awq_build.build()
     torch.cuda.set_device(local)
+    numa = bind_to_gpu_numa_node(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist.barrier()
@@ -462,7 +491,10 @@ def run_cuda(args):
                     "steps": e2e_steps, "ms_per_step": sec_e2e * 1e3, "steps_in_flight": E2E_DEPTH,
                     "one_step_at_a_time_ms": sec_e2e_serial * 1e3,
                     "one_step_at_a_time_value": world * wbytes / sec_e2e_serial / 1e12,
-                    "outputs_equal_device_resident": bool(e2e_matches)},
+                    "outputs_equal_device_resident": bool(e2e_matches),
+                    "host_binding": numa,
+                    "pcie_GBps_per_gpu": (sum(m * k * 2 for _, (k, n) in shapes()) +
+                                          sum(m * n * 2 for _, (k, n) in shapes())) / sec_e2e / 1e9},
             "gpu_launches": launches_per_step * args.steps,
             "device_status": status_after_timed,
             "clocks": sampler.summary(t_wall0, t_wall1),
