@@ -268,7 +268,12 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * sorted_ids was built with an expert_map, i.e. some (token, slot) pairs have no expert here and
  * contribute zero; bit 1 says w13_q and w2_q are decode-layout copies (awq_b200_repack_qweight
  * over all E * H, respectively E * I, stacked rows), which only the weight-streaming kernels
- * read: block 8 or 16 and group 128, anything else returns AWQ_B200_ERR_SHAPE.
+ * read: block 8 or 16 and group 128, anything else returns AWQ_B200_ERR_SHAPE; bit 2 selects the
+ * direct mode for a handful of pairs (T * topk <= AWQ_B200_MOE_DIRECT_MAX_PAIRS, block 8, no
+ * expert_map): no permutation is needed - expert_ids is the routed-id table topk_ids [T * topk]
+ * itself, sorted_ids and num_post_pad are ignored (may be NULL), sorted_capacity must be
+ * T * topk * 8 (one 8-row block per pair) - which takes awq_b200_moe_align_block_size out of the
+ * chain for the decode of one or two tokens.
  * Scratch, 256-byte aligned: the activation and per-pair buffers are laid out for
  * round_up(sorted_capacity, block) rows, so the size needed follows the sorted_capacity passed
  * here.  awq_b200_moe_workspace_bytes(T, topk, E', H, I) bounds it when sorted_capacity is
@@ -277,6 +282,7 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * layout returns AWQ_B200_ERR_WORKSPACE before anything is launched.
  * Requires H % 128 == 0, I % 128 == 0, group in {32, 64, 128}.
  */
+#define AWQ_B200_MOE_DIRECT_MAX_PAIRS 16
 int awq_b200_moe_block_size(int T, int topk, int E, int H, int I, int group);
 
 size_t awq_b200_moe_workspace_bytes(int T, int topk, int E, int H, int I);

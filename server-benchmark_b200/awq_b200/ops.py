@@ -20,6 +20,7 @@ import torch
 from . import _lib
 
 PACK_FACTOR = 8
+MOE_DIRECT_MAX_PAIRS = 16     # AWQ_B200_MOE_DIRECT_MAX_PAIRS
 
 
 def _stream() -> int:
@@ -387,10 +388,21 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
     if w1_decode is not None and block in (8, 16) and g == 128:
         w13_q, w2_q = w1_decode, w2_decode
         flags |= 2
-    sorted_ids, expert_ids, num_post = moe_align_block_size(
-        topk_ids, block, n_global, expert_map, ignore_invalid_experts=True)
     need = lib.awq_b200_moe_workspace_bytes(t, topk, n_global, h, inter)
     ws = _workspace(hidden_states.device, need)
+    if expert_map is None and block == 8 and t * topk <= MOE_DIRECT_MAX_PAIRS:
+        # a handful of pairs: one row block per pair straight from topk_ids, no permutation
+        rc = lib.awq_b200_moe_experts(
+            hidden_states.data_ptr(), w13_q.data_ptr(), w13_s.data_ptr(), w13_z.data_ptr(),
+            w2_q.data_ptr(), w2_s.data_ptr(), w2_z.data_ptr(), topk_weights.data_ptr(),
+            None, topk_ids.data_ptr(), None, out.data_ptr(),
+            t, topk, e, h, inter, g, block, flags | 4, t * topk * 8,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            _stream())
+        _lib.check("awq_b200_moe_experts", rc)
+        return out
+    sorted_ids, expert_ids, num_post = moe_align_block_size(
+        topk_ids, block, n_global, expert_map, ignore_invalid_experts=True)
     rc = lib.awq_b200_moe_experts(
         hidden_states.data_ptr(), w13_q.data_ptr(), w13_s.data_ptr(), w13_z.data_ptr(),
         w2_q.data_ptr(), w2_s.data_ptr(), w2_z.data_ptr(), topk_weights.data_ptr(),

@@ -365,15 +365,25 @@ static int moe_validate(const void* x, const void* w13_q, const void* w13_s, con
                         int topk, int E, int H, int I, int group, int block, int expert_parallel,
                         int64_t sorted_capacity, const void* workspace, size_t workspace_bytes,
                         size_t limit, awq::MoeArgs* args) {
+  const bool direct = (expert_parallel & 4) != 0;
   if (!x || !w13_q || !w13_s || !w13_z || !w2_q || !w2_s || !w2_z || !topk_weights ||
-      !sorted_ids || !expert_ids || !num_post_pad || !out)
+      !expert_ids || !out)
     return AWQ_B200_ERR_NULL;
+  if (!direct && (!sorted_ids || !num_post_pad)) return AWQ_B200_ERR_NULL;
   if (T < 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0 || block <= 0) return AWQ_B200_ERR_SHAPE;
+  if (direct) {
+    // no permutation: one 8-row block per pair, expert_ids is the routed-id table itself
+    if (block != 8 || (expert_parallel & 1) || (int64_t)T * topk > AWQ_B200_MOE_DIRECT_MAX_PAIRS)
+      return AWQ_B200_ERR_SHAPE;
+    if (sorted_capacity != (int64_t)T * topk * 8) return AWQ_B200_ERR_WORKSPACE;
+    sorted_ids = nullptr;
+    num_post_pad = nullptr;
+  }
   if (group != 128 && group != 64 && group != 32) return AWQ_B200_ERR_GROUP;
   if (!awq::moe_supported(H, I, group, block)) return AWQ_B200_ERR_SHAPE;
   if ((int64_t)T * topk > (1 << 24)) return AWQ_B200_ERR_LIMIT;
   if ((sorted_capacity + block - 1) / block > 65535) return AWQ_B200_ERR_LIMIT;
-  if (sorted_capacity < awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block))
+  if (!direct && sorted_capacity < awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block))
     return AWQ_B200_ERR_WORKSPACE;
   *args = awq::MoeArgs{static_cast<const __half*>(x),
                        static_cast<const uint32_t*>(w13_q),

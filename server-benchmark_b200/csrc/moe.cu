@@ -239,6 +239,16 @@ moe_align_kernel(const int32_t* __restrict__ ids, int numel, int E, int block,
 
 constexpr bool kMoeExact = false;  // conversion used by the expert GEMMs (see stream_core.cuh)
 
+// Direct mode (no permutation; sorted_ids == nullptr): row block `blk` holds the single pair
+// `blk` in its row 0, and expert_ids is the flat [T * topk] table of routed expert ids itself.
+// For a handful of pairs (decode of one or two tokens) this drops the permutation kernel from
+// the chain; a pair that shares its expert with another one then reads that expert's weights
+// again, which costs less than the launch it saves.
+__device__ __forceinline__ int row_pair(const int32_t* sorted_ids, int pos0, int row, int blk,
+                                        int numel) {
+  return sorted_ids ? sorted_ids[pos0 + row] : (row == 0 ? blk : numel);
+}
+
 struct Gemm1Params {
   const __half* x;           // [T, H]
   const uint32_t* w13_q;     // [E, H, 2I/8]
@@ -268,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(co
   pdl_wait();  // the routing tables come from the kernels before this one
   // uniform over the cluster: nobody reaches a cluster barrier if the block is unused
   // both loads in flight together (expert_ids covers every block of the grid)
-  const int post = p.num_post_pad[0];
+  const int post = p.num_post_pad ? p.num_post_pad[0] : 0x7fffffff;
   const int e = p.expert_ids[blk];
   if (pos0 >= post || e < 0) return;
 
@@ -303,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(co
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
       const int row = (tid >> 4) + 8 * j;
-      const int fid = p.sorted_ids[pos0 + row];
+      const int fid = row_pair(p.sorted_ids, pos0, row, blk, p.numel);
       src.xvalid[j] = fid < p.numel;
       const int token = src.xvalid[j] ? fid / p.topk : 0;
       src.xsrc[j] = p.x + (size_t)token * p.H + (tid & 15) * 8;
@@ -384,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(co
   pdl_launch_dependents();
   pdl_wait();
   // both loads in flight together (expert_ids covers every block of the grid)
-  const int post = p.num_post_pad[0];
+  const int post = p.num_post_pad ? p.num_post_pad[0] : 0x7fffffff;
   const int e = p.expert_ids[blk];
   if (pos0 >= post || e < 0) return;
 
@@ -396,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(co
   const uint32_t* wq = p.w2_q + (size_t)e * p.I * words;
   const uint32_t* wz = p.w2_z + (size_t)e * groups * words;
   const __half* ws = p.w2_s + (size_t)e * groups * p.H;
-  if (tid < 8 * MT) s_fid[tid] = p.sorted_ids[pos0 + tid];
+  if (tid < 8 * MT) s_fid[tid] = row_pair(p.sorted_ids, pos0, tid, blk, p.numel);
 
   TileSrc<MT> src;
   {
@@ -414,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(co
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
       const int row = (tid >> 4) + 8 * j;
-      src.xvalid[j] = p.sorted_ids[pos0 + row] < p.numel;
+      src.xvalid[j] = row_pair(p.sorted_ids, pos0, row, blk, p.numel) < p.numel;
       src.xsrc[j] = p.act + (size_t)(pos0 + row) * p.I + (tid & 15) * 8;
     }
     const int wcol = word0 + 8 * warp + g;

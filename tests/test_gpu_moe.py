@@ -135,6 +135,31 @@ def test_fused_experts_vs_oracle(A, e, h, i, t, k):
     assert O.rel_err(y2, ref) < TOL
 
 
+@pytest.mark.parametrize("t,k,e,h,i", [(1, 8, 128, 2048, 768), (2, 8, 128, 2048, 768),
+                                       (3, 4, 16, 512, 256), (1, 2, 8, 256, 128)])
+def test_direct_mode_for_a_handful_of_pairs_equals_the_permuted_path(A, t, k, e, h, i):
+    """Up to 16 (token, slot) pairs skip the permutation kernel (one row block per pair, experts
+    read from topk_ids).  An identity expert_map forces the permuted path: same bits."""
+    w1, w2, x, logits = _moe_case(e, h, i, t, k, seed=40 + t)
+    w1d = tuple(a.cuda() for a in w1)
+    w2d = tuple(a.cuda() for a in w2)
+    wts, ids, _ = A.fused_topk(x.cuda(), logits.cuda(), k, True)
+    direct = A.fused_experts(x.cuda(), w1d, w2d, wts, ids)
+    permuted = A.fused_experts(x.cuda(), w1d, w2d, wts, ids, global_num_experts=e,
+                               expert_map=torch.arange(e, dtype=torch.int32, device="cuda"))
+    assert torch.equal(direct, permuted)
+    # two slots of one token on the same expert: the pair blocks stay independent
+    ids2 = ids.clone()
+    ids2[:, 1] = ids2[:, 0]
+    direct2 = A.fused_experts(x.cuda(), w1d, w2d, wts, ids2)
+    permuted2 = A.fused_experts(x.cuda(), w1d, w2d, wts, ids2, global_num_experts=e,
+                                expert_map=torch.arange(e, dtype=torch.int32, device="cuda"))
+    assert torch.equal(direct2, permuted2)
+    ref = O.fused_experts_fp32(x.numpy(), *[a.numpy() for a in w1], *[a.numpy() for a in w2],
+                               wts.cpu().numpy(), ids2.cpu().numpy())
+    assert O.rel_err(direct2.float().cpu().numpy(), ref) < TOL
+
+
 def test_wna16_layout_converts_back_bit_exact(A, golden):
     """uint8 [E, N, K/2] (vLLM's MoE WNA16 layout) -> AWQ layout on the device: vLLM's own
     converted tensors give back the AWQ tensors they were made from, and stacked random experts
