@@ -84,20 +84,6 @@ struct WtParams {
   int half_cols;               // MODE 1: I (gate columns [0, I), up columns [I, 2 I))
 };
 
-__device__ __forceinline__ uint32_t wt_lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-// four adjacent 8-column groups in one instruction (x4): registers 4 c .. 4 c + 3 go to group c
-__device__ __forceinline__ void wt_tmem_st_x4(uint32_t taddr, const uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-      : "memory");
-}
 __device__ __forceinline__ void wt_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -108,15 +94,6 @@ __device__ __forceinline__ void wt_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) 
       : "r"(taddr)
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void wt_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 __device__ __forceinline__ __half2 dup_lo(uint32_t v) { return as_half2(prmt(v, v, 0x1010)); }
 __device__ __forceinline__ __half2 dup_hi(uint32_t v) { return as_half2(prmt(v, v, 0x3232)); }
@@ -271,8 +248,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                               (uint64_t)(((step & 3) * 32) >> 4);
           const uint32_t acc = (j > 0 || step > 0) ? 1u : 0u;
           const uint32_t acol = tmem_u + kWtColA + (par * 8 + step) * 16;
-          wt_umma_ts(tmem_u, acol, db, idesc, acc);
-          wt_umma_ts(tmem_u + NT, acol + 8, db, idesc, acc);
+          umma_f16_ts(tmem_u, acol, db, idesc, acc);
+          umma_f16_ts(tmem_u + NT, acol + 8, db, idesc, acc);
         }
       };
       tc_fence_after();
@@ -382,7 +359,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int e = 0; e < 4; ++e) {
         const uint32_t rowA = wsm + (16 * (4 * h + e)) * 64;
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) w[e][rr] = wt_lds32(rowA + off[rr]);
+        for (int rr = 0; rr < 4; ++rr) w[e][rr] = lds32(rowA + off[rr]);
       }
       // the MMAs of stage j - 2 must have read this half of the A ring
       if (j >= 2) ok = mbar_wait(a_empty(par), (uint32_t)(((j >> 1) - 1) & 1), &s_abort, 35);
@@ -419,8 +396,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         // half-quarter hq of this warp's lanes; steps 4 h + 2 sp2, + 1; both tiles
         const uint32_t a_slot = tmem + lane_q + kWtColA + (par * 8 + 4 * h + 2 * sp2) * 16;
-        wt_tmem_st_x4(a_slot, frag[0]);
-        wt_tmem_st_x4(a_slot + (16u << 16), frag[1]);
+        tmem_st_16x256b_x4(a_slot, frag[0]);
+        tmem_st_16x256b_x4(a_slot + (16u << 16), frag[1]);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
