@@ -54,10 +54,11 @@ UNIT = "TB/s"
 M_TOKENS = 16
 GROUP = 128
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the M = 16 kernel, as a ratio to the
-# launch's algorithmic bytes, from an ncu capture of a smaller case (K = 8192, N = 29568: 130.2 MB
-# of traffic for 126.6 MB); the traffic of the full-size launches is scaled by their bytes
-NCU_TRAFFIC_RATIO = 1.028
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two M = 16 kernels, as a ratio to
+# the launch's algorithmic bytes, from ncu captures of smaller cases (gemm_ts: K = 8192, N = 29568,
+# 130.2 MB of traffic for 126.6 MB; gemm_q8: K = 8192, N = 36864, 164.0 MB for 158.6 MB); the
+# traffic of the full-size launches is scaled by their bytes
+NCU_TRAFFIC_RATIO = {"gemm_ts": 1.028, "gemm_q8": 1.034}
 E2E_DEPTH = 4          # steps in flight in the end-to-end leg
 TIMED_SECONDS = 0.6    # what the repeated device-resident measurement covers at least
 ROTATE_BYTES = 400_000_000  # weight sets rotated per shape: at least this much and at least two
@@ -481,7 +482,11 @@ def run_cuda(args):
                              f"{name}: {kn}" for (name, _), kn in zip(shapes(), kernels)) +
                                    "; achieved = int4 weight bytes of the step / step time",
                          "achieved_all_bytes": achieved_all,
-                         "traffic": NCU_TRAFFIC_RATIO * all_bytes_per_step(m),
+                         "traffic": sum(
+                             NCU_TRAFFIC_RATIO["gemm_q8" if "q8" in kn else "gemm_ts"] *
+                             (k * n // 2 + (k // GROUP) * n * 2 + (k // GROUP) * (n // 8) * 4 +
+                              m * k * 2 + m * n * 2)
+                             for (_, (k, n)), kn in zip(shapes(), kernels)),
                          "traffic_basis": "per step (sum of the step's launches); achieved is per "
                                           "step as well"},
             "cpu_baseline": cpu,
