@@ -400,7 +400,8 @@ static int moe_validate(const void* x, const void* w13_q, const void* w13_s, con
                        T, topk, E, H, I, group, block,
                        sorted_capacity,
                        expert_parallel & 1,
-                       (expert_parallel >> 1) & 1};
+                       (expert_parallel >> 1) & 1,
+                       direct ? 1 : 0};
   // the scratch need follows sorted_capacity, which the caller chose (it is at least the
   // minimum for the stacked expert count, larger if the permutation was built for more experts)
   const size_t need = awq::moe_layout_bytes(*args);

@@ -237,7 +237,9 @@ struct MoeArgs {
   int64_t sorted_capacity;
   int expert_parallel;
   int decode_layout;  // w13_q / w2_q are decode-layout copies (blocks of 8 or 16 rows only)
+  int direct;         // no permutation: one 8-row block per pair, expert_ids = routed-id table
 };
+constexpr int kMoeDirectTicketBytes = 4096;  // AWQ_B200_MOE_DIRECT_MAX_PAIRS tokens x 64 slabs
 bool moe_supported(int H, int I, int group, int block);
 size_t moe_workspace_bytes(int T, int topk, int E, int H, int I);
 int moe_block_size(int T, int topk, int E, int H, int I, int group);

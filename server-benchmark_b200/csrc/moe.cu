@@ -259,6 +259,8 @@ struct Gemm1Params {
   const int32_t* num_post_pad;
   __half* act;               // [capacity, I] in permuted row order
   int numel, topk, H, I, group;
+  uint32_t* tickets;         // direct mode: counters the down GEMM uses, cleared here; else nullptr
+  int n_tickets;
 };
 
 // MT = token tiles of 8 per row block: 1 (8-row blocks, decode-size batches: almost every expert
@@ -276,6 +278,11 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm1_kernel(co
   const int pos0 = blk * (8 * MT);
   pdl_launch_dependents();
   pdl_wait();  // the routing tables come from the kernels before this one
+  if (p.tickets != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    // every kernel that used the counters before has completed (pdl_wait); the down GEMM of this
+    // call starts counting only after this kernel has
+    for (int i = threadIdx.x; i < p.n_tickets; i += kThreads) p.tickets[i] = 0u;
+  }
   // uniform over the cluster: nobody reaches a cluster barrier if the block is unused
   // both loads in flight together (expert_ids covers every block of the grid)
   const int post = p.num_post_pad ? p.num_post_pad[0] : 0x7fffffff;
@@ -380,6 +387,9 @@ struct Gemm2Params {
   const int32_t* num_post_pad;
   __half* pair_out;          // [T * topk, H]
   int numel, H, I, group;
+  uint32_t* tickets;         // direct mode: one counter per (token, column slab); else nullptr
+  __half* out;               // direct mode: [T, H], written by the cluster that finishes a token's
+  int topk;                  //              last pair for a slab
 };
 
 template <int MT, int GROUP, bool RP>
@@ -472,6 +482,41 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 5 : 4) moe_gemm2_kernel(co
     }
   }
   cluster.sync();
+  // Direct mode: the sum over a token's slots is done here instead of in moe_sum_kernel.  The
+  // cluster that finishes a token's last pair for this column slab adds the topk rows in slot
+  // order (the same fp32 sum of the stored fp16 values, so the result does not depend on which
+  // cluster comes last).
+  if (p.tickets != nullptr && rank == 0) {
+    __shared__ int s_last;
+    const int token = blk / p.topk;
+    if (tid == 0) {
+      __threadfence();
+      const unsigned t = atomicAdd(p.tickets + token * gridDim.y + blockIdx.y, 1u);
+      s_last = t == (unsigned)p.topk - 1u;
+      if (s_last) __threadfence();
+    }
+    __syncthreads();
+    if (s_last) {
+      for (int u = tid; u < kBN / 8; u += kThreads) {
+        const int n = blockIdx.y * kBN + u * 8;
+        if (n >= p.H) continue;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        for (int sl = 0; sl < p.topk; ++sl) {
+          const uint4 r = __ldcg(reinterpret_cast<const uint4*>(
+              p.pair_out + ((size_t)token * p.topk + sl) * p.H + n));
+          const __half* h = reinterpret_cast<const __half*>(&r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += __half2float(h[j]);
+        }
+        __align__(16) __half o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(v[j]);
+        *reinterpret_cast<uint4*>(p.out + (size_t)token * p.H + n) = *reinterpret_cast<uint4*>(o);
+      }
+    }
+  }
 }
 
 // out[t, h] = sum_slot pair_out[t * topk + slot, h]; one thread per 8 columns.
@@ -623,7 +668,7 @@ size_t moe_workspace_bytes(int T, int topk, int E, int H, int I) {
   const int64_t cap = awq_b200_moe_sorted_capacity((int64_t)T * topk, E, block);
   const int64_t rows = (cap + block - 1) / block * block;
   const size_t small = align_up((size_t)rows * I * sizeof(__half), 256) +
-                       align_up((size_t)T * topk * H * sizeof(__half), 256);
+                       align_up((size_t)T * topk * H * sizeof(__half), 256) + kMoeDirectTicketBytes;
   if (moe_block_size(T, topk, E, H, I, 128) == 128) {
     const size_t big = moe_tc_workspace_bytes(T, topk, E, H, I);
     return big > small ? big : small;
@@ -638,12 +683,13 @@ size_t moe_layout_bytes(const MoeArgs& a) {
   if (a.block == 128) return moe_tc_layout_bytes(a);
   const int64_t rows = (a.sorted_capacity + a.block - 1) / a.block * a.block;
   return align_up((size_t)rows * a.I * sizeof(__half), 256) +
-         align_up((size_t)a.T * a.topk * a.H * sizeof(__half), 256);
+         align_up((size_t)a.T * a.topk * a.H * sizeof(__half), 256) +
+         (a.direct ? (size_t)kMoeDirectTicketBytes : 0);
 }
 
 template <int MT, int GROUP, bool RP>
-int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel, int nblk,
-                     cudaStream_t stream) {
+int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, uint32_t* tickets, int numel,
+                     int nblk, cudaStream_t stream) {
   constexpr int smem = Cfg<MT>::kSmemBytes;
   static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
@@ -659,7 +705,8 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
   }
   {
     Gemm1Params p{a.x, a.w13_q, a.w13_s, a.w13_z, a.sorted_ids, a.expert_ids, a.num_post_pad,
-                  act, numel, a.topk, a.H, a.I, a.group};
+                  act, numel, a.topk, a.H, a.I, a.group, tickets,
+                  tickets ? a.T * ((a.H + kBN - 1) / kBN) : 0};
     const int slabs = (a.I + 127) / 128;
     const int S = pick_cluster(slabs * nblk, a.H / kBK);
     if (int rc = launch_clustered(moe_gemm1_kernel<MT, GROUP, RP>, p, dim3(S, slabs, nblk), S, smem, stream))
@@ -667,7 +714,7 @@ int launch_moe_gemms(const MoeArgs& a, __half* act, __half* pair_out, int numel,
   }
   {
     Gemm2Params p{act, a.w2_q, a.w2_s, a.w2_z, a.topk_weights, a.sorted_ids, a.expert_ids,
-                  a.num_post_pad, pair_out, numel, a.H, a.I, a.group};
+                  a.num_post_pad, pair_out, numel, a.H, a.I, a.group, tickets, a.out, a.topk};
     const int slabs = (a.H + kBN - 1) / kBN;
     const int S = pick_cluster(slabs * nblk, a.I / kBK);
     if (int rc = launch_clustered(moe_gemm2_kernel<MT, GROUP, RP>, p, dim3(S, slabs, nblk), S, smem, stream))
@@ -689,6 +736,11 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
   __half* act = static_cast<__half*>(workspace);
   __half* pair_out = reinterpret_cast<__half*>(static_cast<uint8_t*>(workspace) +
                                                align_up((size_t)rows * a.I * sizeof(__half), 256));
+  // direct mode: the down GEMM sums a token's slots itself when the counters fit
+  uint32_t* tickets = nullptr;
+  if (a.direct && (size_t)a.T * ((a.H + kBN - 1) / kBN) * sizeof(uint32_t) <= kMoeDirectTicketBytes)
+    tickets = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(pair_out) +
+                                          align_up((size_t)numel * a.H * sizeof(__half), 256));
 
   if (a.expert_parallel) {
     // pairs routed to experts of other ranks are never written: they must read as zero
@@ -697,16 +749,16 @@ int launch_moe_experts(const MoeArgs& a, void* workspace, size_t workspace_bytes
   }
   int rc;
   if (a.decode_layout)
-    rc = a.block == 8 ? launch_moe_gemms<1, 128, true>(a, act, pair_out, numel, nblk, stream)
-                      : launch_moe_gemms<2, 128, true>(a, act, pair_out, numel, nblk, stream);
+    rc = a.block == 8 ? launch_moe_gemms<1, 128, true>(a, act, pair_out, tickets, numel, nblk, stream)
+                      : launch_moe_gemms<2, 128, true>(a, act, pair_out, tickets, numel, nblk, stream);
   else if (a.group == 128)
-    rc = a.block == 8 ? launch_moe_gemms<1, 128, false>(a, act, pair_out, numel, nblk, stream)
-                      : launch_moe_gemms<2, 128, false>(a, act, pair_out, numel, nblk, stream);
+    rc = a.block == 8 ? launch_moe_gemms<1, 128, false>(a, act, pair_out, tickets, numel, nblk, stream)
+                      : launch_moe_gemms<2, 128, false>(a, act, pair_out, tickets, numel, nblk, stream);
   else
-    rc = a.block == 8 ? launch_moe_gemms<1, 0, false>(a, act, pair_out, numel, nblk, stream)
-                      : launch_moe_gemms<2, 0, false>(a, act, pair_out, numel, nblk, stream);
+    rc = a.block == 8 ? launch_moe_gemms<1, 0, false>(a, act, pair_out, tickets, numel, nblk, stream)
+                      : launch_moe_gemms<2, 0, false>(a, act, pair_out, tickets, numel, nblk, stream);
   if (rc) return rc;
-  {
+  if (tickets == nullptr) {
     const long long work = (long long)a.T * (a.H / 8);
     if (launch_pdl(moe_sum_kernel, dim3((unsigned)((work + 255) / 256)), dim3(256), 0, stream,
                    (const __half*)pair_out, a.out, a.T, a.topk, a.H) != cudaSuccess) {
