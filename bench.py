@@ -652,7 +652,10 @@ def run_moe(dev, stream):
     block_of = lambda t: _lib.load().awq_b200_moe_block_size(t, k, e, h, i, GROUP)  # noqa: E731
     awq_b200.reserve_workspace(awq_b200.moe_workspace_bytes(max(synth.MOE_TOKENS), k, e, h, i), dev)
     out = []
-    for t in synth.MOE_TOKENS:
+    from awq_b200 import ops as awq_ops
+    # the benchmark's token counts, plus the few-token decode points where the direct mode (no
+    # permutation kernel, slot sum inside the down GEMM) competes with the permuted chain
+    for t in sorted(set(synth.MOE_TOKENS) | {2, 4, 8}):
         x = synth.activations(t, h).to(dev)
         logits = synth.gating_logits(t, e).to(dev)
         _, ids, _ = awq_b200.fused_topk(x, logits, k, True)
@@ -666,6 +669,16 @@ def run_moe(dev, stream):
         row = {"T": t, "experts_hit": hit, "us": round(sec * 1e6, 1),
                "GBps": round(byts / sec / 1e9, 1),
                "TFLOPs": round(t * 75497472 / sec / 1e12, 2)}
+        if t * k <= 64:
+            # both chains at the few-token points: pairs at or below the limit go direct
+            keep = awq_ops.MOE_DIRECT_MAX_PAIRS
+            for name, limit in (("us_direct", 64), ("us_permuted", 0)):
+                awq_ops.MOE_DIRECT_MAX_PAIRS = limit
+                sm = graph_time([(lambda L=L: awq_b200.fused_moe(x, L[0], L[1], logits, k, True))
+                                 for L in layers], stream, reps=reps)
+                row[name] = round(sm * 1e6, 1)
+            awq_ops.MOE_DIRECT_MAX_PAIRS = keep
+            row["direct_by_default"] = t * k <= keep
         if block_of(t) in (8, 16):
             # the same layer with the optional decode-layout copies of the expert weights
             def layer(L):

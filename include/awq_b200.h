@@ -285,7 +285,7 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * layout returns AWQ_B200_ERR_WORKSPACE before anything is launched.
  * Requires H % 128 == 0, I % 128 == 0, group in {32, 64, 128}.
  */
-#define AWQ_B200_MOE_DIRECT_MAX_PAIRS 16
+#define AWQ_B200_MOE_DIRECT_MAX_PAIRS 64
 int awq_b200_moe_block_size(int T, int topk, int E, int H, int I, int group);
 
 size_t awq_b200_moe_workspace_bytes(int T, int topk, int E, int H, int I);

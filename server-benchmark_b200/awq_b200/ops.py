@@ -20,7 +20,8 @@ import torch
 from . import _lib
 
 PACK_FACTOR = 8
-MOE_DIRECT_MAX_PAIRS = 16     # AWQ_B200_MOE_DIRECT_MAX_PAIRS
+MOE_DIRECT_MAX_PAIRS = 16     # pairs up to which fused_experts goes direct (the C ABI takes
+                              # up to AWQ_B200_MOE_DIRECT_MAX_PAIRS = 64)
 
 
 def _stream() -> int:
