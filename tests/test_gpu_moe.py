@@ -155,6 +155,8 @@ def test_direct_mode_for_a_handful_of_pairs_equals_the_permuted_path(A, t, k, e,
                                expert_map=torch.arange(e, dtype=torch.int32, device="cuda"))
     assert torch.equal(direct, permuted)
     # two slots of one token on the same expert: the pair blocks stay independent
+    if k == 1:
+        return
     ids2 = ids.clone()
     ids2[:, 1] = ids2[:, 0]
     direct2 = A.fused_experts(x.cuda(), w1d, w2d, wts, ids2)
