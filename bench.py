@@ -882,7 +882,8 @@ def recorded_serving():
         if parsed:
             runs.append({"file": "profiles/serving/" + name, "gpus": int(mt.group(2)),
                          "kernels": "stock vLLM (Marlin), same seeded weights" if mt.group(4)
-                         else "this package (plug-in)",
+                         else "this package (plug-in)" +
+                         (", decode-layout copies of the weights" if "decode-copies" in name else ""),
                          "concurrency": int(mt.group(6)), **parsed})
     return {"source": "recorded result files (not measured by this invocation)",
             "workload": "Qwen3-30B-A3B architecture, random-init AWQ, 1000 in / 1000 out, "
