@@ -171,10 +171,10 @@ def cpu_model() -> str:
     return "unknown"
 
 
-def cpu_reference_sample(reps: int):
+def cpu_reference_sample(reps: int, warmup: int = 3):
     """Times the fp32 dequantise-then-matmul of the o_proj shape (K = N = 8192, M = 16) on the
     host, and the matmul alone on the already dequantised matrix.  Returns a dict with the best
-    and the mean of `reps` calls (after one warm-up) for both."""
+    and the mean of `reps` calls (after `warmup` untimed ones) for both."""
     import torch
     from awq_b200 import synth
     from oracle import awq_oracle as O
@@ -184,7 +184,8 @@ def cpu_reference_sample(reps: int):
     k, n = 8192, 8192
     qw, s, qz = synth.awq_linear_tensors(k, n, GROUP, seed=0)
     x = synth.activations(M_TOKENS, k, seed=0)
-    O.awq_gemm_fp32_torch(x, qw, s, qz, GROUP)  # warm-up
+    for _ in range(max(1, warmup)):
+        O.awq_gemm_fp32_torch(x, qw, s, qz, GROUP)
     times = []
     for _ in range(reps):
         t = time.perf_counter()
@@ -202,7 +203,7 @@ def cpu_reference_sample(reps: int):
             "matmul_only_best": min(mm), "cpu_model": cpu_model(),
             "sample": f"o_proj K=8192 N=8192 M={M_TOKENS} group 128, torch fp32 "
                       f"dequantise+matmul on {cores} threads, best and mean of {reps} calls "
-                      "after one warm-up"}
+                      f"after {max(1, warmup)} warm-up calls"}
 
 
 def cpu_baseline_block(c):
@@ -218,12 +219,13 @@ def run_reference(args):
     if rank != 0:
         return
     reps = max(3, min(args.steps, 20))
-    c = cpu_reference_sample(reps)
+    warm = max(3, min(args.warmup, 5))      # a step is about 0.1 s of host time
+    c = cpu_reference_sample(reps, warm)
     block = cpu_baseline_block(c)
     val = block["value"]
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": reps, "warmup": 1, "ms_per_step": c["best"] * 1e3, "higher_is_better": True,
+        "steps": reps, "warmup": warm, "ms_per_step": c["best"] * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "awq_w4a16_linear_M16_qwen2.5-72b_layer (sampled: o_proj shape)",
                    "group_size": GROUP, "tokens": M_TOKENS},

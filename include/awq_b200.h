@@ -276,7 +276,9 @@ int awq_b200_moe_align_block_size(const int32_t* topk_ids, int T, int topk, int 
  * chain for the decode of one or two tokens; the down GEMM then also adds a token's slots itself
  * (the cluster that finishes the token's last pair for a column slab, counted in 4 KB of
  * counters at the end of the scratch layout that the first GEMM of the call clears), so the chain
- * is two launches.  Every routed id must be a valid expert index in this mode.
+ * is two launches.  Every routed id must be a valid expert index in this mode, and the scratch
+ * need (one 8-row block per pair) exceeds the bound of awq_b200_moe_workspace_bytes once
+ * T * topk * 8 > awq_b200_moe_sorted_capacity(T * topk, E, 16): size the buffer for the layout.
  * Scratch, 256-byte aligned: the activation and per-pair buffers are laid out for
  * round_up(sorted_capacity, block) rows, so the size needed follows the sorted_capacity passed
  * here.  awq_b200_moe_workspace_bytes(T, topk, E', H, I) bounds it when sorted_capacity is

@@ -20,8 +20,10 @@ import torch
 from . import _lib
 
 PACK_FACTOR = 8
-MOE_DIRECT_MAX_PAIRS = 16     # pairs up to which fused_experts goes direct (the C ABI takes
-                              # up to AWQ_B200_MOE_DIRECT_MAX_PAIRS = 64)
+MOE_DIRECT_MAX_PAIRS = 64     # pairs up to which fused_experts goes direct (the limit of the C ABI,
+                              # AWQ_B200_MOE_DIRECT_MAX_PAIRS; measured on the Qwen3-30B-A3B layer:
+                              # 25 / 33 / 42 / 67 us direct against 30 / 35 / 46 / 74 us through the
+                              # permutation at 1 / 2 / 4 / 8 tokens)
 
 
 def _stream() -> int:
@@ -391,7 +393,10 @@ def fused_experts(hidden_states: torch.Tensor, w1, w2, topk_weights: torch.Tenso
         flags |= 2
     need = lib.awq_b200_moe_workspace_bytes(t, topk, n_global, h, inter)
     ws = _workspace(hidden_states.device, need)
-    if expert_map is None and block == 8 and t * topk <= MOE_DIRECT_MAX_PAIRS:
+    if (expert_map is None and block == 8 and t * topk <= MOE_DIRECT_MAX_PAIRS
+            and t * topk * 8 <= lib.awq_b200_moe_sorted_capacity(t * topk, n_global, 16)):
+        # (the last condition: the scratch bound of awq_b200_moe_workspace_bytes covers one 8-row
+        # block per pair only while the pairs are few compared with the experts)
         # a handful of pairs: one row block per pair straight from topk_ids, no permutation
         rc = lib.awq_b200_moe_experts(
             hidden_states.data_ptr(), w13_q.data_ptr(), w13_s.data_ptr(), w13_z.data_ptr(),

@@ -138,7 +138,8 @@ def test_fused_experts_vs_oracle(A, e, h, i, t, k):
 @pytest.mark.parametrize("t,k,e,h,i", [(1, 8, 128, 2048, 768), (2, 8, 128, 2048, 768),
                                        (3, 4, 16, 512, 256), (1, 2, 8, 256, 128),
                                        (4, 8, 128, 2048, 768), (8, 8, 128, 2048, 768),
-                                       (5, 8, 16, 8192, 256), (64, 1, 16, 8192, 256)])
+                                       (5, 8, 16, 8192, 256), (64, 1, 64, 8192, 256),
+                                       (64, 1, 16, 512, 256)])
 def test_direct_mode_for_a_handful_of_pairs_equals_the_permuted_path(A, t, k, e, h, i, monkeypatch):
     """A handful of (token, slot) pairs skip the permutation kernel (one row block per pair,
     experts read from topk_ids) and the slot sum happens inside the down GEMM (or, when the
