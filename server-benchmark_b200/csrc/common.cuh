@@ -27,6 +27,37 @@ inline bool pdl_enabled() {
   static const bool on = getenv("AWQ_B200_NO_PDL") == nullptr;
   return on;
 }
+// How many clusters of `S` CTAs (x dimension) of `kernel` the GPU holds at once.  A cluster must
+// find all its SMs free inside one GPC, so odd sizes pack badly: a grid with more clusters than
+// this runs in waves.  `cache` holds one answer per size (0 = not asked yet); an answer the
+// runtime cannot give counts as "enough".  The kernel's dynamic shared-memory limit must have
+// been raised before the first call.
+template <typename Kernel>
+inline int resident_clusters(Kernel kernel, int S, int threads, size_t smem,
+                             std::atomic<int>* cache) {
+  if (S < 1 || S > 8) return 1 << 30;
+  const int known = cache[S];
+  if (known > 0) return known;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S, 1024, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int got = 0;
+  if (cudaOccupancyMaxActiveClusters(&got, kernel, &cfg) != cudaSuccess || got <= 0) {
+    (void)cudaGetLastError();
+    got = 1 << 30;
+  }
+  cache[S] = got;
+  return got;
+}
+
 // Plain (non-cluster) launch with the attribute.  The kernel must execute pdl_wait before it
 // touches anything an earlier kernel writes or reads.
 template <typename... KArgs, typename... Args>

@@ -546,35 +546,6 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
-// How many clusters of `S` CTAs of this kernel the GPU holds at once (cached per device and size;
-// 0 = not asked yet).  An answer the runtime cannot give counts as "enough".
-template <typename Kernel>
-int resident_clusters(Kernel kernel, int S) {
-  static std::atomic<int> cache[64][9];   // zero-initialised
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || S < 1 || S > 8) return 1 << 30;
-  const int n = cache[dev][S];
-  if (n > 0) return n;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(S, 1024, 1);
-  cfg.blockDim = dim3(kTsThreads, 1, 1);
-  cfg.dynamicSmemBytes = kTsSmemBytes;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = S;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int got = 0;
-  if (cudaOccupancyMaxActiveClusters(&got, kernel, &cfg) != cudaSuccess || got <= 0) {
-    (void)cudaGetLastError();
-    got = 1 << 30;
-  }
-  cache[dev][S] = got;
-  return got;
-}
-
 template <bool EXACT>
 int launch_ts(const CUtensorMap& map_w, const CUtensorMap& map_x, const TsParams& p,
               cudaStream_t stream) {
@@ -602,7 +573,8 @@ int launch_ts(const CUtensorMap& map_w, const CUtensorMap& map_x, const TsParams
     S = slots / slabs;
     S = S > 8 ? 8 : S;
     while (S > 1 && KT / S < 4) --S;
-    while (S > 1 && resident_clusters(kernel, S) < slabs) --S;
+    static std::atomic<int> resident[64][9];  // zero-initialised: not asked yet
+    while (S > 1 && resident_clusters(kernel, S, kTsThreads, kTsSmemBytes, resident[dev]) < slabs) --S;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S, slabs, 1);

@@ -535,6 +535,14 @@ int launch_wt_kernel(const CUtensorMap& map_w, const CUtensorMap& map_x, const W
       return AWQ_B200_ERR_LAUNCH;
     attr_done[dev] = true;
   }
+  if (MODE == 0 && S > 1) {
+    // the K split only as wide as lets every cluster of the grid be resident at once
+    static std::atomic<int> resident[64][9];  // zero-initialised: not asked yet
+    const int clusters = (int)(grid.y * grid.z);
+    while (S > 1 && resident_clusters(kernel, S, kWtThreads, C::kSmemBytes, resident[dev]) < clusters)
+      --S;
+    grid.x = S;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kWtThreads, 1, 1);
