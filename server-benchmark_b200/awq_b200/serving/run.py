@@ -32,6 +32,22 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _wait_for_front(proc, base: str, timeout_s: float = 120.0) -> None:
+    """The front answers /front/stats once it listens."""
+    import urllib.request
+    deadline = time.time() + timeout_s
+    while True:
+        if proc.poll() is not None:
+            raise RuntimeError(f"the front exited with {proc.returncode}")
+        try:
+            urllib.request.urlopen(base + "/front/stats", timeout=5).read()
+            return
+        except Exception:
+            if time.time() > deadline:
+                raise TimeoutError("the front did not come up")
+            time.sleep(0.5)
+
+
 def topology_text(args, ports: list[int], cmds: list[list[str]], envs: list[dict]) -> str:
     """What the compose file says in the reference: one entry per instance with its GPUs, port
     and command, then the front."""
@@ -116,7 +132,7 @@ def run(args) -> dict:
                         os.environ.get("PYTHONPATH", ""))
             front = subprocess.Popen(fcmd, env=fenv, start_new_session=True)
             base = f"http://127.0.0.1:{fport}"
-            time.sleep(2.0)
+            _wait_for_front(front, base)
         else:
             base = f"http://127.0.0.1:{ports[0]}"
         benv = dict(os.environ, CUDA_VISIBLE_DEVICES="", HF_HUB_OFFLINE="1",

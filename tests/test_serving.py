@@ -260,3 +260,88 @@ def test_plugin_classes_pickle_by_reference():
     cfg = vllm_methods.B200AWQConfig(4, 128, True)
     back = pickle.loads(pickle.dumps(cfg))
     assert type(back) is vllm_methods.B200AWQConfig and back.group_size == 128
+
+
+FAKE_SERVER = r'''
+import sys
+from aiohttp import web
+port = int(sys.argv[sys.argv.index("--port") + 1])
+async def health(r): return web.Response(text="ok")
+async def models(r): return web.json_response({"object": "list", "data": [{"id": "m"}]})
+async def chat(r):
+    body = await r.json()
+    return web.json_response({"choices": [{"message": {"content": "w1 w2"}}], "echo": body.get("n")})
+app = web.Application()
+app.router.add_get("/health", health); app.router.add_get("/v1/models", models)
+app.router.add_post("/v1/chat/completions", chat)
+web.run_app(app, host="127.0.0.1", port=port, print=None, access_log=None)
+'''
+
+FAKE_CLIENT = r'''
+import sys, json, urllib.request
+base = sys.argv[sys.argv.index("--base-url") + 1]
+conc = sys.argv[sys.argv.index("--max-concurrency") + 1]
+for n in range(4):      # really goes through the endpoint (and the front, when there is one)
+    req = urllib.request.Request(base + "/v1/chat/completions", data=json.dumps({"n": n}).encode(),
+                                 headers={"Content-Type": "application/json"})
+    assert json.loads(urllib.request.urlopen(req, timeout=20).read())["echo"] == n
+print("noise before the block")
+print("============ Serving Benchmark Result ============")
+print("Successful requests:                     4")
+print("Maximum request concurrency:             " + conc)
+print("Request throughput (req/s):              1.50")
+print("Output token throughput (tok/s):         100.00")
+print("Total token throughput (tok/s):          " + str(200 + int(conc)) + ".00")
+print("Mean TTFT (ms):                          10.00")
+print("Mean TPOT (ms):                          5.00")
+print("==================================================")
+'''
+
+
+def test_run_orchestrates_replicas_front_and_client(tmp_path, monkeypatch):
+    """serving.run.run from start to finish with stand-ins for the two vLLM programs: two fake
+    servers on their GPU slices, the real front, a fake client that talks through it; the result
+    files come out in the reference's layout and a second run skips them."""
+    import sys
+    server = tmp_path / "fake_server.py"
+    server.write_text(FAKE_SERVER)
+    fake_client = tmp_path / "fake_client.py"
+    fake_client.write_text(FAKE_CLIENT)
+    seen_env = []
+
+    def fake_serve_command(model_dir_, served, port, tp_, pp_, extra):
+        return [sys.executable, str(server), "x", "--port", str(port), "--model", model_dir_]
+
+    real_env = replicas.replica_env
+
+    def spy_env(i, per, plugin, seed, options=None):
+        env = real_env(i, per, plugin, seed, options)
+        seen_env.append((i, env["CUDA_VISIBLE_DEVICES"], env.get("AWQ_B200_DUMMY_FILL")))
+        return env
+
+    def fake_benchmark_command(model, base, inp, out, conc, prompts, tokenizer=None):
+        return [sys.executable, str(fake_client), "x", "--base-url", base, "--max-concurrency",
+                str(conc), "--num-prompts", str(prompts)]
+
+    monkeypatch.setattr(replicas, "serve_command", fake_serve_command)
+    monkeypatch.setattr(replicas, "replica_env", spy_env)
+    monkeypatch.setattr(client, "benchmark_command", fake_benchmark_command)
+    args = run.parser().parse_args([
+        "--instances", "2", "--concurrency", "4,8", "--num-prompts", "4", "--num-layers", "1",
+        "--results-dir", str(tmp_path / "results"), "--work-dir", str(tmp_path / "work"),
+        "--startup-timeout", "60", "--client-timeout", "60", "--seed", "3"])
+    out = run.run(args)
+    assert out["server"] == "b200_x_2" and len(out["runs"]) == 2
+    assert [r["concurrency"] for r in out["runs"]] == [4, 8]
+    assert [r["total_token_throughput"] for r in out["runs"]] == [204.0, 208.0]
+    assert sorted(seen_env) == [(0, "0", "3"), (1, "1", "3")]
+    for r in out["runs"]:
+        text = open(r["result_file"]).read()
+        assert text.startswith(client.RESULT_HEADER) and "noise before" not in text
+        assert re.search(REFERENCE_PATTERNS["total"], text)
+        assert "vllm_0:" in text and "vllm_1:" in text and "front:" in text
+        assert "============ Benchmark Command ============" in text
+        name = r["result_file"].rsplit("/", 1)[1]
+        assert re.match(REFERENCE_FILENAME, name[:-len(".txt")].rsplit("_vllm_benchmark", 1)[0])
+    again = run.run(args)
+    assert all(r.get("skipped") == "result exists" for r in again["runs"])
