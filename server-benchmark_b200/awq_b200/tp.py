@@ -158,13 +158,19 @@ class PeerAllReduce:
         with torch.cuda.device(self.device):
             base = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)      # AWQ_B200_IPC_HANDLE_BYTES
-            _lib.check("awq_b200_peer_region_create",
-                       lib.awq_b200_peer_region_create(size, ctypes.byref(base), handle))
-            self._base = base.value
+            # a failure on one rank must not leave the others alone in a collective: every rank
+            # goes through the same sequence (gather, agreement, barrier) whatever happens to it
+            rc = lib.awq_b200_peer_region_create(size, ctypes.byref(base), handle)
+            failure = None if rc == 0 else f"rank {self.rank} could not create its region (code {rc})"
+            self._base = base.value if rc == 0 else None
             handles = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            ptrs, failure = [], None
+            dist.all_gather_object(handles, handle.raw if rc == 0 else None, group=group)
+            if failure is None and any(h is None for h in handles):
+                failure = "another rank could not create its region"
+            ptrs = []
             for r in range(self.world):
+                if failure is not None:
+                    break
                 if r == self.rank:
                     ptrs.append(self._base)
                     continue
@@ -181,10 +187,12 @@ class PeerAllReduce:
             if int(ok[0]) == 0:
                 for p in self._opened:
                     lib.awq_b200_peer_region_close(ctypes.c_void_p(p))
+                self._opened = []
                 dist.barrier(group=group)
-                lib.awq_b200_peer_region_destroy(ctypes.c_void_p(self._base))
+                if self._base is not None:
+                    lib.awq_b200_peer_region_destroy(ctypes.c_void_p(self._base))
                 self._base = None
-                raise RuntimeError(failure or "a peer could not map the regions")
+                raise RuntimeError(failure or "another rank could not map the regions")
         self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
         # this rank's region as a tensor, so that the GEMM can be given a view of it as `out`
         self.region = torch.as_tensor(_DeviceBytes(self._base, size), device=self.device)
