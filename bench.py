@@ -841,6 +841,32 @@ def run_tp(args, world, rank, dev, stream, barrier):
         sec_peer = timed(g3.replay, steps)
         step_peer()                    # the replays left the call numbering consistent
         torch.cuda.synchronize()
+    # the exchange alone (no GEMM in front of it): 20 calls per replayed graph, fp16 [M, 8192]
+    alone = None
+    if comm is not None:
+        try:
+            calls = 20
+            xa = torch.randn(m, 8192, device=dev).half()
+
+            def peer_alone():
+                for i in range(calls):
+                    comm.reduce(i & 1, m, 8192)
+
+            def nccl_alone():
+                for i in range(calls):
+                    dist.all_reduce(xa)
+
+            alone = {}
+            for name, body in (("peer_us", peer_alone), ("nccl_us", nccl_alone)):
+                body()
+                torch.cuda.synchronize()
+                ga = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(ga, stream=stream):
+                    body()
+                alone[name] = round(timed(ga.replay, max(10, steps // 10)) / calls * 1e6, 2)
+                del ga
+        except Exception as e:
+            alone = {"note": f"{type(e).__name__}: {str(e)[:100]}"}
     sec = min(x for x in (sec_graph, sec_eager, sec_peer) if x is not None)
     res = {"parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": sec * 1e3,
            "ms_per_step_graph_peer_all_reduce": None if sec_peer is None else sec_peer * 1e3,
@@ -850,6 +876,7 @@ def run_tp(args, world, rank, dev, stream, barrier):
            "peer_all_reduce": "one-shot kernel over peer-mapped regions, GEMM writes its partial "
                               "into the region (awq_b200_allreduce)" if comm is not None
                               else f"unavailable: {comm_note}",
+           "exchange_alone": alone,
            "device_status": _device_status(),
            "ms_per_step_eager": sec_eager * 1e3,
            "ms_per_step_graph": None if sec_graph is None else sec_graph * 1e3,
