@@ -174,3 +174,47 @@ def test_reference_arm_prints_the_contract_line():
         assert key in line, key
     assert line["value"] > 0 and line["cpu_baseline"]["kind"] in ("port", "reference")
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def test_validation_of_the_newer_entry_points_without_gpu(built_library):
+    """Exchange, layout conversion and the direct MoE mode refuse bad arguments before any CUDA
+    call."""
+    from awq_b200 import _lib
+    lib = _lib.load()
+    buf = (ctypes.c_char * 8192)()
+    p = (ctypes.addressof(buf) + 255) & ~255
+    regions = (ctypes.c_void_p * 2)(p, p)
+    # all-reduce: rank count, rank, offsets, sizes, NULLs, alignment
+    assert lib.awq_b200_allreduce(regions, 0, 9, 4096, p, 32, p, 0, None) == -2
+    assert lib.awq_b200_allreduce(regions, 2, 2, 4096, p, 32, p, 0, None) == -2
+    assert lib.awq_b200_allreduce(regions, 0, 2, 16, p, 32, p, 0, None) == -2      # inside the flags
+    assert lib.awq_b200_allreduce(regions, 0, 2, 4096, p, 24, p, 0, None) == -2    # not 16-byte units
+    assert lib.awq_b200_allreduce(None, 0, 2, 4096, p, 32, p, 0, None) == -1
+    assert lib.awq_b200_allreduce(regions, 0, 2, 4096, p, 32, None, 0, None) == -1
+    assert lib.awq_b200_allreduce(regions, 0, 2, 4096, p, 0, p, 0, None) == 0      # nothing to do
+    odd = (ctypes.c_void_p * 2)(p, p + 8)
+    assert lib.awq_b200_allreduce(odd, 0, 2, 4096, p, 32, p, 0, None) == -3
+    hole = (ctypes.c_void_p * 2)(p, None)
+    assert lib.awq_b200_allreduce(hole, 0, 2, 4096, p, 32, p, 0, None) == -1
+    # peer regions
+    out = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    assert lib.awq_b200_peer_region_create(100, ctypes.byref(out), handle) == -2   # below the flag area
+    assert lib.awq_b200_peer_region_create(8192, None, handle) == -1
+    assert lib.awq_b200_peer_region_open(None, ctypes.byref(out)) == -1
+    assert lib.awq_b200_peer_region_close(None) == -1
+    # MoE WNA16 layout conversion
+    assert lib.awq_b200_wna16_to_awq(p, p, p, p, p, p, 1, 12, 128, 128, None) == -2   # N % 8
+    assert lib.awq_b200_wna16_to_awq(p, p, p, p, p, p, 1, 8, 192, 128, None) == -2    # K % group
+    assert lib.awq_b200_wna16_to_awq(p, p, None, p, p, p, 1, 8, 128, 128, None) == -1
+    # direct MoE mode: block 8 only, not with an expert map, bounded pair count, exact capacity
+    T, topk, E, H, I = 2, 8, 128, 2048, 768
+    base = [p] * 7 + [p, None, p, None, p]
+    tail = lambda block, flags, cap: [T, topk, E, H, I, 128, block, flags, cap, p, 1 << 30, None]  # noqa: E731
+    assert lib.awq_b200_moe_experts(*base, *tail(16, 4, T * topk * 8)) == -2
+    assert lib.awq_b200_moe_experts(*base, *tail(8, 5, T * topk * 8)) == -2
+    assert lib.awq_b200_moe_experts(*base, *tail(8, 4, T * topk * 8 + 8)) == -5
+    many = [p] * 7 + [p, None, p, None, p] + [16, topk, E, H, I, 128, 8, 4, 16 * topk * 8, p, 1 << 30, None]
+    assert lib.awq_b200_moe_experts(*many) == -2                                   # 128 pairs > 64
+    # without the flag the permutation tables are required
+    assert lib.awq_b200_moe_experts(*base, *tail(8, 0, T * topk * 8)) == -1
