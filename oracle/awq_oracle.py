@@ -140,6 +140,30 @@ def pack_kmajor(qweight, group: int = 128) -> np.ndarray:
     return np.ascontiguousarray((t[..., 0::2] | (t[..., 1::2] << 4)).astype(np.uint8)).reshape(-1)
 
 
+def awq_gemm_fixed_point_model(x, qweight, scales, qzeros, group: int = 128) -> np.ndarray:
+    """Model of the arithmetic of this repository's K-major decode kernel (not a restatement of
+    the reference): every token is rewritten as 24-bit fixed point X = rint(x * 2^22 / amax), the
+    per-group products sum_k q * X are exact integers, and only the fold s * (sum - z * sum_k X)
+    runs in fp32 before the result is scaled back by amax / 2^22.  Tests use it to bound what the
+    fixed-point step may cost against the fp32 reference (it is below fp16's own rounding)."""
+    x = np.asarray(x).astype(np.float32)
+    q = unpack_awq(np.asarray(qweight)).astype(np.int64)          # [K, N]
+    z = unpack_awq(np.asarray(qzeros)).astype(np.float32)         # [K/G, N]
+    s = np.asarray(scales).astype(np.float32)                     # [K/G, N]
+    m, k = x.shape
+    n = q.shape[1]
+    amax = np.abs(x).max(axis=1)
+    inv = np.where(amax > 0, np.float32(4194304.0) / np.maximum(amax, np.float32(1e-30)), 0.0)
+    xi = np.rint(x * inv[:, None].astype(np.float32)).astype(np.int64)      # |X| <= 2^22
+    out = np.zeros((m, n), dtype=np.float32)
+    for g in range(k // group):
+        rows = slice(g * group, (g + 1) * group)
+        v = (xi[:, rows] @ q[rows]).astype(np.float32)            # exact below 2^24 * 15 * 128 ...
+        sx = xi[:, rows].sum(axis=1).astype(np.float32)
+        out += s[g][None, :] * (v - z[g][None, :] * sx[:, None])
+    return out * (amax / np.float32(4194304.0))[:, None].astype(np.float32)
+
+
 def awq_to_wna16_qweight(qweight) -> np.ndarray:
     """AWQ qweight int32 [K, N/8] -> the "standard" layout of vLLM's MoE WNA16 method:
     uint8 [N, K/2], byte (n, j) = nibble(k=2j) | nibble(k=2j+1) << 4

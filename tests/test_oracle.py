@@ -161,3 +161,24 @@ def test_wna16_layout_against_vllm_converter():
         assert np.array_equal(g[f"{name}.wna16_scales"], g[f"{name}.scales"].T)
         assert np.array_equal(O.wna16_to_awq_qweight(w), g[f"{name}.qweight"])
         assert np.array_equal(O.wna16_to_awq_qzeros(z), g[f"{name}.qzeros"])
+
+
+def test_fixed_point_model_of_the_kmajor_kernel_stays_below_fp16_rounding():
+    """What rewriting the activations as 24-bit fixed point per token may cost: against the fp32
+    reference the model is off by well under fp16's own rounding of the output, also when one
+    element of a token is a thousand times larger than the rest."""
+    from awq_b200 import synth
+    k, n, m = 1024, 256, 16
+    qw, s, qz = synth.awq_linear_tensors(k, n, 128, seed=3)
+    x = synth.activations(m, k, seed=4).numpy().astype(np.float32)
+    x[3, 17] = 1000.0           # an outlier sets the token's scale
+    x[5] = 0.0                  # an all-zero token
+    x16 = x.astype(np.float16)
+    ref = O.awq_gemm_fp32(x16, qw.numpy(), s.numpy(), qz.numpy(), 128)
+    got = O.awq_gemm_fixed_point_model(x16, qw.numpy(), s.numpy(), qz.numpy(), 128)
+    assert np.isfinite(got).all() and not got[5].any()
+    assert O.rel_err(got, ref) < 1e-4
+    for t in range(m):          # per token too: the outlier row keeps its accuracy
+        denom = np.abs(ref[t]).max()
+        if denom > 0:
+            assert np.abs(got[t] - ref[t]).max() / denom < 2e-4
